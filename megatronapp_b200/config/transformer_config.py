@@ -189,6 +189,10 @@ class TransformerConfig(ModelParallelConfig):
     moe_router_num_groups: Optional[int] = None
     moe_router_group_topk: Optional[int] = None
     moe_router_pre_softmax: bool = False
+    # how a group of experts is ranked under group-limited routing: "topk_sum" (sum of its best topk / group_topk scores)
+    # or "max" (its single best score); and whether the chosen pre-softmax scores are divided by their sum
+    moe_router_group_score: str = "topk_sum"
+    moe_router_renormalize: bool = False
     moe_router_topk_scaling_factor: Optional[float] = None
     moe_router_score_function: str = "softmax"
     moe_router_dtype: Optional[str] = None
@@ -305,6 +309,8 @@ class TransformerConfig(ModelParallelConfig):
         if self.cp_comm_type is not None and isinstance(self.cp_comm_type, list):
             if len(self.cp_comm_type) != self.num_layers:
                 raise ValueError("cp_comm_type list must have num_layers entries")
+        if self.moe_router_group_score not in ("topk_sum", "max"):
+            raise ValueError("moe_router_group_score must be topk_sum | max")
         if self.kernel_backend not in ("auto", "b200", "torch"):
             raise ValueError("kernel_backend must be auto | b200 | torch")
 

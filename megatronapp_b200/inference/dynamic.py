@@ -9,6 +9,13 @@ Design here: every step runs ONE forward over a flat token batch ``[T, 1, h]`` t
 cache is one ``[num_blocks * block_size, groups, head_dim]`` tensor per layer; a request owns a list of
 blocks, a token at position ``p`` lives in slot ``table[p // bs] * bs + p % bs``.  Attention gathers the
 request's slots (padded over requests), so admission, retirement and preemption never move KV data.
+
+Layers need not be softmax attention with their own K/V.  Latent-attention layers page one latent vector per token
+(``attend_latent``), and a layer may read the pages another layer wrote.  Recurrent mixers keep a fixed-size state per
+request instead of pages: every request owns a *state row* for its lifetime (``recurrent_state`` hands out per-layer
+tensors ``[max_requests, ...]`` indexed by that row, zeroed when the row is given to a new request), and ``packed``
+describes the step's sequence boundaries and rows to the scan kernels.  Chunked prefill, continuous batching and
+preemption-by-recompute therefore work unchanged for hybrid models.
 """
 from __future__ import annotations
 
@@ -49,6 +56,7 @@ class BlockAllocator:
 class _Seq:
     blocks: List[int] = field(default_factory=list)
     kv_len: int = 0            # tokens whose K/V are in the cache
+    state_row: int = -1        # row of this request in the recurrent-state tensors
 
 
 class DynamicInferenceContext:
@@ -60,6 +68,11 @@ class DynamicInferenceContext:
         self.allocator = BlockAllocator(num_blocks)
         self.seqs: Dict[str, _Seq] = {}
         self.kv: Dict[int, tuple] = {}                 # layer -> (K, V) [num_blocks*bs, ng, hn]
+        self.latents: Dict[int, torch.Tensor] = {}     # layer -> latent pages [num_blocks*bs, rank]
+        self.states: Dict[object, torch.Tensor] = {}   # key -> recurrent state [max_requests, ...]
+        self._free_rows = list(range(max_requests - 1, -1, -1))
+        self.packed = None                             # ops.seqmix.PackedBatch of the current step
+        self._device = None
         self.use_paged_kernel = os.environ.get("B200_PAGED_ATTN", "1") == "1"     # 0: gather + einsum reference path
         self.kernel_calls = 0
         # per-step plan (set by begin_step)
@@ -82,12 +95,25 @@ class DynamicInferenceContext:
         return max(0, -(-total // self.block_size) - have)
 
     def add_request(self, rid: str):
-        self.seqs[rid] = _Seq()
+        if not self._free_rows:
+            raise RequestOverflowError(f"more than max_requests={self.max_requests} concurrent requests")
+        row = self._free_rows.pop()
+        for t in self.states.values():                 # the row's previous owner left its state behind
+            t[row].zero_()
+        self.seqs[rid] = _Seq(state_row=row)
 
     def release(self, rid: str):
         s = self.seqs.pop(rid, None)
         if s:
             self.allocator.release(s.blocks)
+            self._free_rows.append(s.state_row)
+
+    def recurrent_state(self, key, shape, dtype) -> torch.Tensor:
+        """The per-request state tensor ``[max_requests, *shape]`` of one layer (zeros for a request's first token)."""
+        t = self.states.get(key)
+        if t is None:
+            t = self.states[key] = torch.zeros(self.max_requests, *shape, dtype=dtype, device=self._device)
+        return t
 
     def _slot(self, s: _Seq, pos: torch.Tensor) -> torch.Tensor:
         table = torch.tensor(s.blocks, dtype=torch.long)
@@ -97,8 +123,11 @@ class DynamicInferenceContext:
     def begin_step(self, work: List[tuple], device) -> torch.Tensor:
         """``work = [(rid, n_new)]``: reserve blocks, build the gather / scatter indices and the mask of the
         packed batch.  Returns the absolute positions ``[T]`` of the new tokens."""
+        from ..ops.seqmix import PackedBatch
+
         plan, pos_all, slots_all = [], [], []
         q0 = 0
+        self._device = device
         for rid, n_new in work:
             s = self.seqs[rid]
             if s.kv_len + n_new > self.max_sequence_length:
@@ -125,6 +154,7 @@ class DynamicInferenceContext:
             mask[i, :n, :L] = torch.arange(L).unsqueeze(0) <= qpos
             mask[i, n:, 0] = True                                      # padded query rows: keep softmax finite
         self._plan = plan
+        self.packed = PackedBatch([p[1] for p in plan] + [q0], [self.seqs[p[0]].state_row for p in plan], device)
         # paged-attention kernel inputs: the request row and the number of visible keys of every packed query token, and
         # the block tables of this step's requests
         max_blocks = max(len(self.seqs[p[0]].blocks) for p in plan)
@@ -152,6 +182,25 @@ class DynamicInferenceContext:
 
     def last_token_index(self) -> Dict[str, int]:
         return {rid: qs + n - 1 for rid, qs, n, _ in self._plan}
+
+    # -- latent attention over the paged cache ----------------------------------------
+    def attend_latent(self, layer: int, q_lat: torch.Tensor, c_new: Optional[torch.Tensor], scale: float) -> torch.Tensor:
+        """``q_lat [T, H, r]`` (queries carried into the latent space) against the latent pages of ``layer``.  ``c_new
+        [T, r]`` are this step's latents, written into their pages first; a layer that shares another layer's latents
+        passes ``None`` and names that layer (whose pages this step already holds).  Returns the softmax-weighted sum of
+        latents, fp32 ``[T, H, r]``."""
+        from ..ops import seqmix
+
+        if c_new is not None:
+            if layer not in self.latents:
+                self.latents[layer] = torch.zeros(self.num_blocks * self.block_size, c_new.shape[-1], dtype=c_new.dtype,
+                                                  device=c_new.device)
+            self.latents[layer][self._write_slots] = c_new
+        elif layer not in self.latents:
+            raise RuntimeError(f"layer {layer} has written no latents for this step")
+        self.kernel_calls += 1
+        return seqmix.latent_attention_paged(q_lat, self.latents[layer], self._block_table, self._tok_req, self._tok_len,
+                                             self.block_size, scale)
 
     # -- attention over the paged cache --------------------------------------------
     def attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:
@@ -409,17 +458,16 @@ class DynamicInferenceEngine:
             self._preempt_one()
 
     @torch.no_grad()
-    def step(self) -> List[InferenceRequest]:
-        self._admit()
-        work = self._plan()
-        if not work:
-            return []
+    def forward_tokens(self, work: List[tuple]):
+        """One forward over a packed batch.  ``work = [(rid, tokens)]``: the next tokens of requests the context knows
+        (``context.add_request``); they are appended to what the cache and the recurrent state already hold.  Returns
+        ``(logits [T, V] or None off the last pipeline stage, {rid: index of its last token in the batch})``; the row of
+        request ``k``'s ``j``-th token is ``sum(len(tokens) of requests before k) + j``."""
         ctx = self.context
         dev = next(self.model.parameters()).device
         self.model.eval()
-        positions = ctx.begin_step(work, dev)
-        ids = torch.tensor([t for rid, n in work for t in self.running[rid].tokens[self.running[rid].fed:self.running[rid].fed + n]],
-                           dtype=torch.long, device=dev).unsqueeze(0)
+        positions = ctx.begin_step([(rid, len(toks)) for rid, toks in work], dev)
+        ids = torch.tensor([t for _, toks in work for t in toks], dtype=torch.long, device=dev).unsqueeze(0)
         inner = self.model
         while hasattr(inner, "module"):
             inner = inner.module
@@ -429,6 +477,18 @@ class DynamicInferenceEngine:
         last = ctx.last_token_index()
         ctx.end_step()
         self.steps += 1
+        return logits, last
+
+    @torch.no_grad()
+    def step(self) -> List[InferenceRequest]:
+        self._admit()
+        work = self._plan()
+        if not work:
+            return []
+        ctx = self.context
+        dev = next(self.model.parameters()).device
+        logits, last = self.forward_tokens([(rid, self.running[rid].tokens[self.running[rid].fed:self.running[rid].fed + n])
+                                            for rid, n in work])
         finished = []
         vocab = getattr(self.tokenizer, "vocab_size", None)
         eod = self.tokenizer.eod

@@ -102,8 +102,14 @@ def sort_chunks_by_idxs(x, split_sizes, sorted_idxs):
     return torch.cat([chunks[i] for i in (sorted_idxs.tolist() if torch.is_tensor(sorted_idxs) else sorted_idxs)], dim=0)
 
 
-def group_limited_topk(scores, topk, num_tokens, num_experts, num_groups, group_topk):
-    group_scores = scores.view(num_tokens, num_groups, -1).topk(max(1, topk // group_topk), dim=-1)[0].sum(dim=-1)
+def group_limited_topk(scores, topk, num_tokens, num_experts, num_groups, group_topk, group_score="topk_sum"):
+    """Only experts of the ``group_topk`` best groups compete.  A group ranks by the sum of its best
+    ``topk // group_topk`` scores (``"topk_sum"``) or by its single best score (``"max"``)."""
+    per_group = scores.view(num_tokens, num_groups, -1)
+    if group_score == "max":
+        group_scores = per_group.amax(dim=-1)
+    else:
+        group_scores = per_group.topk(max(1, topk // group_topk), dim=-1)[0].sum(dim=-1)
     group_idx = torch.topk(group_scores, k=group_topk, dim=-1, sorted=False)[1]
     group_mask = torch.zeros_like(group_scores).scatter_(1, group_idx, 1)
     score_mask = group_mask.unsqueeze(-1).expand(num_tokens, num_groups, num_experts // num_groups).reshape(num_tokens, -1)
@@ -113,18 +119,21 @@ def group_limited_topk(scores, topk, num_tokens, num_experts, num_groups, group_
 
 def topk_softmax_with_capacity(logits, topk, capacity_factor=None, pad_to_capacity=False, drop_policy="probs",
                                use_pre_softmax=False, num_groups=None, group_topk=None, scaling_factor=None,
-                               deterministic_mode=False, score_function="softmax", expert_bias=None):
+                               deterministic_mode=False, score_function="softmax", expert_bias=None,
+                               group_score="topk_sum", renormalize=False):
     n, E = logits.shape
 
     def _topk(scores):
         if group_topk:
-            return group_limited_topk(scores, topk, n, E, num_groups, group_topk)
+            return group_limited_topk(scores, topk, n, E, num_groups, group_topk, group_score)
         return torch.topk(scores, k=topk, dim=1)
 
     if score_function == "softmax":
         if use_pre_softmax:
             scores = torch.softmax(logits, dim=-1, dtype=torch.float32).type_as(logits)
             probs, top_idx = _topk(scores)
+            if renormalize:
+                probs = probs / (probs.sum(dim=-1, keepdim=True) + 1e-20)
         else:
             sc, top_idx = _topk(logits)
             probs = torch.softmax(sc, dim=-1, dtype=torch.float32).type_as(logits)

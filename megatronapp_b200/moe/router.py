@@ -89,7 +89,17 @@ class TopKRouter(MegatronModule):
         fused_ok = (logits.is_cuda and self.score_function == "softmax" and cfg.moe_expert_capacity_factor is None
                     and not cfg.moe_router_group_topk and self.expert_bias is None and self.num_experts <= 256
                     and self.topk <= 8 and logits.dtype in (torch.float32, torch.bfloat16, torch.float16))
-        if fused_ok:
+        grouped_ok = (self.score_function == "softmax" and cfg.moe_router_pre_softmax and cfg.moe_router_group_topk
+                      and cfg.moe_router_group_score == "max" and cfg.moe_expert_capacity_factor is None
+                      and self.expert_bias is None and not cfg.moe_router_topk_scaling_factor and not self.training)
+        if grouped_ok:
+            # one warp per token: softmax, groups ranked by their best expert, top-k inside the kept groups
+            from ..ops.seqmix import group_limited_router
+
+            probs, rmap = group_limited_router(logits.float(), self.topk, cfg.moe_router_num_groups,
+                                               cfg.moe_router_group_topk, bool(cfg.moe_router_renormalize))
+            tpe = None
+        elif fused_ok:
             # one warp per token: softmax + top-k (+ renormalisation / scaling), dense probs + routing map out
             from ..ops.moe import router_topk
 
@@ -117,7 +127,7 @@ class TopKRouter(MegatronModule):
             logits, self.topk, cfg.moe_expert_capacity_factor, cfg.moe_pad_expert_input_to_capacity,
             cfg.moe_token_drop_policy, cfg.moe_router_pre_softmax, cfg.moe_router_num_groups,
             cfg.moe_router_group_topk, cfg.moe_router_topk_scaling_factor, cfg.deterministic_mode,
-            self.score_function, self.expert_bias)
+            self.score_function, self.expert_bias, cfg.moe_router_group_score, cfg.moe_router_renormalize)
 
     def forward(self, x):
         x = self.apply_input_jitter(x)

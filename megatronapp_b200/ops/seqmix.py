@@ -1,0 +1,297 @@
+"""Sequence-mixing ops over a *packed* token batch: recurrent matrix memories, their short convolutions, latent
+attention over a paged cache, group-limited routing, and the fp32-residual norms that surround them.
+
+Packed batch: tokens of all sequences lie one after another along the first axis; ``cu`` (``[R + 1]``) holds the
+sequence boundaries, ``slots`` (``[R]``) the row of every sequence in the state tensors.  A sequence may be a whole
+prompt, a portion of one, or a single decoded token: what came before lives in the state row (or the paged cache),
+which every op reads first and leaves updated.
+
+Every op has a sm_100a kernel (``csrc/seqmix/*.cu`` in ``megatronapp_b200/_C_seq.so``) and a PyTorch fp32 path for
+CPU tensors.  CUDA tensors never take the PyTorch path: a missing extension raises.
+
+What is computed in fp32 whatever the activation dtype: the residual stream, norm statistics, decays and gates, the
+recurrent state, attention scores and softmax weights, router scores.
+"""
+from __future__ import annotations
+
+import importlib.util
+from collections import Counter
+from pathlib import Path
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+import torch.nn.functional as F
+
+_EXT = None
+_EXT_ERR: Optional[BaseException] = None
+kernel_calls: Counter = Counter()
+
+
+def _load_ext():
+    global _EXT, _EXT_ERR
+    if _EXT is not None or _EXT_ERR is not None:
+        return _EXT
+    so = Path(__file__).resolve().parent.parent / "_C_seq.so"
+    try:
+        if not so.exists():
+            from ..build import build_seq
+
+            build_seq()
+        spec = importlib.util.spec_from_file_location("megatronapp_b200._C_seq", str(so))
+        mod = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(mod)
+        _EXT = mod
+    except BaseException as e:  # noqa: BLE001 - surfaced by ext()
+        _EXT_ERR = e
+    return _EXT
+
+
+def ext():
+    m = _load_ext()
+    if m is None:
+        raise RuntimeError(f"megatronapp_b200._C_seq (sm_100a extension) is not available: {_EXT_ERR!r}")
+    return m
+
+
+def have_ext() -> bool:
+    return _load_ext() is not None
+
+
+def _i32(x, device) -> torch.Tensor:
+    if torch.is_tensor(x):
+        return x.to(device=device, dtype=torch.int32)
+    return torch.tensor(list(x), dtype=torch.int32, device=device)
+
+
+def _host(x) -> List[int]:
+    return x.tolist() if torch.is_tensor(x) else list(x)
+
+
+class PackedBatch:
+    """Sequence boundaries and state rows of one packed step, on the host and on the device."""
+
+    def __init__(self, cu: Sequence[int], slots: Sequence[int], device):
+        self.cu_host, self.slots_host = _host(cu), _host(slots)
+        self.cu = _i32(self.cu_host, device)
+        self.slots = _i32(self.slots_host, device)
+        self.num_seqs = len(self.slots_host)
+        self.max_len = max((b - a for a, b in zip(self.cu_host[:-1], self.cu_host[1:])), default=0)
+
+    @classmethod
+    def dense(cls, seq_len: int, batch: int, device) -> "PackedBatch":
+        """``batch`` independent sequences of ``seq_len`` tokens, stored sequence after sequence."""
+        return cls([i * seq_len for i in range(batch + 1)], list(range(batch)), device)
+
+
+# ---------------------------------------------------------------------------
+# norms around an fp32 residual stream
+# ---------------------------------------------------------------------------
+
+def add_rms_norm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
+                 out_dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``x`` fp32 ``[T, h]`` (updated in place by ``+ delta`` when given) -> ``(x, rms_norm(x) * weight)``; the
+    normalised copy leaves in ``out_dtype``, the statistics are fp32."""
+    if x.is_cuda:
+        kernel_calls["add_rms_norm"] += 1
+        y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        ext().add_rms_norm(x, delta if delta is None else delta.contiguous(), weight, y, float(eps))
+        return x, y
+    if delta is not None:
+        x.add_(delta.float())
+    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    return x, y.to(out_dtype)
+
+
+def gated_head_rms_norm(o: torch.Tensor, weight: torch.Tensor, gate: Optional[torch.Tensor], eps: float,
+                        out_dtype: torch.dtype) -> torch.Tensor:
+    """``o`` fp32 ``[T, H, dv]``: every head divided by its own root mean square, times ``weight`` (``[dv]`` shared by
+    the heads, or ``[H * dv]``), times ``sigmoid(gate)`` (``[T, H * dv]`` pre-activation) -> ``[T, H * dv]``."""
+    T, H, dv = o.shape
+    if o.is_cuda:
+        kernel_calls["gated_head_rms_norm"] += 1
+        y = torch.empty(T, H * dv, dtype=out_dtype, device=o.device)
+        ext().gated_head_rms_norm(o.contiguous(), weight, None if gate is None else gate.contiguous(), y, float(eps))
+        return y
+    y = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + eps)
+    w = weight.float()
+    y = y * (w.view(1, 1, dv) if w.numel() == dv else w.view(1, H, dv))
+    y = y.reshape(T, H * dv)
+    if gate is not None:
+        y = y * torch.sigmoid(gate.float())
+    return y.to(out_dtype)
+
+
+# ---------------------------------------------------------------------------
+# short causal convolution with a carried window
+# ---------------------------------------------------------------------------
+
+def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: torch.Tensor) -> torch.Tensor:
+    """Depth-wise causal convolution over time followed by SiLU.  ``x [T, C]``, ``weight [C, taps]`` (last column
+    multiplies the current token), ``window [rows, taps - 1, C]``: the inputs that preceded each sequence's first token
+    of this step (zeros at a sequence's start); on return it holds the last ``taps - 1`` inputs seen."""
+    if x.is_cuda:
+        kernel_calls["causal_conv_silu"] += 1
+        y = torch.empty_like(x)
+        ext().causal_conv_silu(x.contiguous(), weight.contiguous(), pb.cu, pb.slots, window, y)
+        return y
+    taps = weight.shape[1]
+    w = weight.float()
+    out = []
+    for r in range(pb.num_seqs):
+        a, b, s = pb.cu_host[r], pb.cu_host[r + 1], pb.slots_host[r]
+        if b == a:
+            continue
+        seq = torch.cat([window[s].float(), x[a:b].float()], dim=0)                # [taps - 1 + n, C]
+        y = sum(seq[j:j + (b - a)] * w[:, j] for j in range(taps))
+        out.append(F.silu(y))
+        if taps > 1:
+            window[s] = seq[-(taps - 1):].to(window.dtype)
+    return torch.cat(out, dim=0).to(x.dtype)
+
+
+# ---------------------------------------------------------------------------
+# gated delta rule with one decay per key channel
+# ---------------------------------------------------------------------------
+
+def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay: torch.Tensor, beta: torch.Tensor,
+                    pb: PackedBatch, state: torch.Tensor, unit_eps: Optional[float] = 1e-6,
+                    q_scale: float = 1.0) -> torch.Tensor:
+    """``q, k [T, KH, d]``, ``v [T, H, dv]``, ``log_decay [T, H, d]`` fp32 (<= 0), ``beta [T, H]`` fp32,
+    ``state [rows, H, d, dv]`` fp32 -> ``o [T, H, dv]`` fp32.  Per head, per token::
+
+        S <- exp(log_decay)[:, None] * S;  u = beta * (v - S^T k);  S <- S + k u^T;  o = S^T q
+
+    Query head ``h`` reads q / k head ``h // (H / KH)``.  With ``unit_eps`` q and k are first scaled to unit length
+    (``x / sqrt(sum x^2 + unit_eps)``); q is then multiplied by ``q_scale``."""
+    T, H, dv = v.shape
+    KH, d = q.shape[1], q.shape[2]
+    if q.is_cuda:
+        kernel_calls["delta_rule_scan"] += 1
+        o = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
+        ext().delta_rule_scan(q.contiguous(), k.contiguous(), v.contiguous(), log_decay.contiguous(), beta.contiguous(),
+                              pb.cu, pb.slots, state, o, -1.0 if unit_eps is None else float(unit_eps), float(q_scale))
+        return o
+    qf, kf, vf = q.float(), k.float(), v.float()
+    if unit_eps is not None:
+        qf = qf * torch.rsqrt(qf.pow(2).sum(-1, keepdim=True) + unit_eps)
+        kf = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + unit_eps)
+    qf = qf * q_scale
+    rep = H // KH
+    if rep > 1:
+        qf, kf = qf.repeat_interleave(rep, dim=1), kf.repeat_interleave(rep, dim=1)
+    decay = torch.exp(log_decay.float())
+    o = torch.empty(T, H, dv, dtype=torch.float32)
+    for r in range(pb.num_seqs):
+        a, b, s = pb.cu_host[r], pb.cu_host[r + 1], pb.slots_host[r]
+        S = state[s].clone()                                                           # [H, d, dv]
+        for t in range(a, b):
+            S = S * decay[t].unsqueeze(-1)
+            u = beta[t].float().unsqueeze(-1) * (vf[t] - torch.einsum("hdv,hd->hv", S, kf[t]))
+            S = S + kf[t].unsqueeze(-1) * u.unsqueeze(1)
+            o[t] = torch.einsum("hdv,hd->hv", S, qf[t])
+        state[s] = S
+    return o
+
+
+# ---------------------------------------------------------------------------
+# mLSTM matrix memory with stabilised exponential gates
+# ---------------------------------------------------------------------------
+
+def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_i: torch.Tensor, log_f: torch.Tensor,
+               pb: PackedBatch, state: torch.Tensor, norm_state: torch.Tensor, max_state: torch.Tensor,
+               q_scale: float = 1.0, denom_eps: float = 1e-6) -> torch.Tensor:
+    """``q, k [T, H, d]``, ``v [T, H, dv]``, log gates ``log_i, log_f [T, H]`` fp32; ``state [rows, H, d, dv]``,
+    ``norm_state [rows, H, d]``, ``max_state [rows, H]`` fp32 (all zero at a sequence's start) -> ``o [T, H, dv]`` fp32::
+
+        m' = max(log_f + m, log_i);  S <- e^(log_f + m - m') S + e^(log_i - m') k v^T;  n likewise with k
+        o = S^T q / (max(|n . q|, e^(-m')) + denom_eps)
+    """
+    T, H, dv = v.shape
+    if q.is_cuda:
+        kernel_calls["mlstm_scan"] += 1
+        o = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
+        ext().mlstm_scan(q.contiguous(), k.contiguous(), v.contiguous(), log_i.contiguous(), log_f.contiguous(),
+                         pb.cu, pb.slots, state, norm_state, max_state, o, float(q_scale), float(denom_eps))
+        return o
+    qf, kf, vf = q.float() * q_scale, k.float(), v.float()
+    li, lf = log_i.float(), log_f.float()
+    o = torch.empty(T, H, dv, dtype=torch.float32)
+    for r in range(pb.num_seqs):
+        a, b, s = pb.cu_host[r], pb.cu_host[r + 1], pb.slots_host[r]
+        S, n, m = state[s].clone(), norm_state[s].clone(), max_state[s].clone()
+        for t in range(a, b):
+            m_new = torch.maximum(lf[t] + m, li[t])
+            keep, put = torch.exp(lf[t] + m - m_new), torch.exp(li[t] - m_new)
+            S = S * keep.view(H, 1, 1) + put.view(H, 1, 1) * kf[t].unsqueeze(-1) * vf[t].unsqueeze(1)
+            n = n * keep.view(H, 1) + put.view(H, 1) * kf[t]
+            m = m_new
+            den = torch.maximum((n * qf[t]).sum(-1).abs(), torch.exp(-m)) + denom_eps
+            o[t] = torch.einsum("hdv,hd->hv", S, qf[t]) / den.unsqueeze(-1)
+        state[s], norm_state[s], max_state[s] = S, n, m
+    return o
+
+
+# ---------------------------------------------------------------------------
+# latent attention over a paged cache of latents
+# ---------------------------------------------------------------------------
+
+def latent_attention_paged(q_lat: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor,
+                           tok_len: torch.Tensor, block_size: int, scale: float) -> torch.Tensor:
+    """Attention of every packed query token over the latents of its own sequence, in the latent space.
+
+    ``q_lat [T, H, r]``: the query of head ``h`` already carried into the latent space (``W_uk,h^T q_h``), so that
+    ``score = q_lat . c * scale``; ``cache [num_slots, r]``: one latent per cached token, pages of ``block_size`` slots;
+    ``block_table [R, max_blocks]``; ``tok_req [T]`` the sequence of each query token, ``tok_len [T]`` how many cached
+    tokens it sees (its own included).  Returns ``sum_j softmax_j(score) c_j`` as fp32 ``[T, H, r]``; the caller applies
+    the per-head value up-projection.  Scores, softmax and the weighted sum are fp32."""
+    T, H, r = q_lat.shape
+    if q_lat.is_cuda:
+        kernel_calls["latent_attention_paged"] += 1
+        o = torch.empty(T, H, r, dtype=torch.float32, device=q_lat.device)
+        ext().latent_attention_paged(q_lat.contiguous(), cache, block_table, tok_req, tok_len, o, int(block_size),
+                                     float(scale))
+        return o
+    o = torch.empty(T, H, r, dtype=torch.float32)
+    req, lens = tok_req.tolist(), tok_len.tolist()
+    t = 0
+    while t < T:                                   # tokens of one sequence are contiguous and see growing prefixes
+        e = t
+        while e + 1 < T and req[e + 1] == req[t]:
+            e += 1
+        L = lens[e]
+        pos = torch.arange(L)
+        slots = block_table[req[t]].long()[pos // block_size] * block_size + pos % block_size
+        c = cache[slots].float()                                                        # [L, r]
+        s = torch.einsum("thr,lr->thl", q_lat[t:e + 1].float(), c) * scale
+        vis = pos.view(1, 1, L) < torch.tensor(lens[t:e + 1]).view(-1, 1, 1)
+        o[t:e + 1] = torch.einsum("thl,lr->thr", torch.softmax(s.masked_fill(~vis, float("-inf")), -1), c)
+        t = e + 1
+    return o
+
+
+# ---------------------------------------------------------------------------
+# router: softmax scores, groups ranked by their best expert, top-k inside the kept groups
+# ---------------------------------------------------------------------------
+
+def group_limited_router(logits: torch.Tensor, topk: int, num_groups: int, keep_groups: int,
+                         renormalize: bool = True) -> Tuple[torch.Tensor, torch.Tensor]:
+    """fp32 ``logits [T, E]`` -> dense ``(probs [T, E] fp32, routing_map [T, E] bool)``: softmax over all experts, a
+    group of neighbouring experts scores as its best member, only experts of the ``keep_groups`` best groups compete
+    for the ``topk`` places; chosen scores are divided by their sum (+ 1e-20) when ``renormalize``."""
+    T, E = logits.shape
+    if logits.is_cuda:
+        kernel_calls["group_limited_router"] += 1
+        probs = torch.zeros(T, E, dtype=torch.float32, device=logits.device)
+        rmap = torch.zeros(T, E, dtype=torch.bool, device=logits.device)
+        ext().group_limited_router(logits.float().contiguous(), probs, rmap, int(topk), int(num_groups), int(keep_groups),
+                                   bool(renormalize))
+        return probs, rmap
+    s = torch.softmax(logits.float(), dim=-1)
+    best = s.view(T, num_groups, E // num_groups).amax(-1)
+    kept = torch.zeros(T, num_groups, dtype=torch.bool).scatter_(1, torch.topk(best, keep_groups, dim=-1).indices, True)
+    masked = s.masked_fill(~kept.repeat_interleave(E // num_groups, dim=1), -1.0)
+    idx = torch.topk(masked, topk, dim=-1).indices
+    w = torch.gather(s, 1, idx)
+    if renormalize:
+        w = w / (w.sum(-1, keepdim=True) + 1e-20)
+    return torch.zeros_like(s).scatter_(1, idx, w), torch.zeros(T, E, dtype=torch.bool).scatter_(1, idx, True)

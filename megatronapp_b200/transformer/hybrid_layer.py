@@ -1,0 +1,74 @@
+"""Pre-norm layer over an fp32 residual stream with an arbitrary sequence mixer, and the block that stacks such layers.
+
+``x <- x + mixer(norm1(x));  x <- x + mlp(norm2(x))`` (the second half is absent for a layer without feed-forward).
+The stream ``x`` stays fp32 whatever the parameter dtype; every addition is fused into the norm that follows it
+(``ResidualRMSNorm``), so a layer hands ``(x, pending)`` to the next one and the block's final norm performs the last
+addition.  The mixer is any module with the ``forward(hidden_states, inference_context=, cross_layer=) -> (out, bias)``
+contract of the framework's attention and recurrent mixers; layers of one block may differ in every size.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional
+
+import torch
+import torch.nn as nn
+
+from ..scan.tracer import scope as _scope
+from .module import MegatronModule
+from .norms import ResidualRMSNorm
+
+
+class ResidualF32Layer(MegatronModule):
+    def __init__(self, config, layer_number: int, mixer: nn.Module, mlp: Optional[nn.Module] = None):
+        super().__init__(config)
+        self.layer_number = layer_number
+        eps = config.layernorm_epsilon
+        self.input_layernorm = ResidualRMSNorm(config, config.hidden_size, eps)
+        self.mixer = mixer
+        self.mlp = mlp
+        self.pre_mlp_layernorm = ResidualRMSNorm(config, config.hidden_size, eps) if mlp is not None else None
+        if mlp is not None and hasattr(mlp, "set_layer_number"):
+            mlp.set_layer_number(layer_number)
+
+    def forward(self, x, pending=None, inference_context=None, cross_layer=None):
+        with _scope("transformer_layer", layer=self.layer_number):
+            x, h = self.input_layernorm(x, pending)
+            out, bias = self.mixer(h, inference_context=inference_context, cross_layer=cross_layer)
+            if bias is not None:
+                out = out + bias
+            if self.mlp is None:
+                return x, out
+            x, h = self.pre_mlp_layernorm(x, out)
+            out, bias = self.mlp(h)
+            if bias is not None:
+                out = out + bias
+        return x, out
+
+
+class ResidualF32Block(MegatronModule):
+    """A stack of ``ResidualF32Layer`` followed by the final norm.  ``layer_builders[i](layer_number)`` returns layer
+    ``i``; ``tap`` (optional callable) receives ``(layer_index, residual_after_layer)`` for inspection tools."""
+
+    def __init__(self, config, layer_builders: List[Callable[[int], ResidualF32Layer]], post_process: bool = True):
+        super().__init__(config)
+        self.layers = nn.ModuleList([build(i) for i, build in enumerate(layer_builders)])
+        self.final_layernorm = ResidualRMSNorm(config, config.hidden_size, config.layernorm_epsilon) if post_process else None
+        self.input_tensor = None
+        self.tap = None
+
+    def set_input_tensor(self, t):
+        self.input_tensor = t
+
+    def forward(self, hidden_states, inference_context=None):
+        x = hidden_states if self.input_tensor is None else self.input_tensor
+        if x.dtype != torch.float32:
+            x = x.float()
+        pending, cross_layer = None, {}
+        for i, layer in enumerate(self.layers):
+            x, pending = layer(x, pending, inference_context=inference_context, cross_layer=cross_layer)
+            if self.tap is not None:
+                self.tap(i, x + pending.float())
+        if self.final_layernorm is None:
+            return x + pending.float()
+        _, h = self.final_layernorm(x, pending)
+        return h

@@ -147,3 +147,95 @@ class MLASelfAttention(MegatronModule):
             ctx = o.permute(2, 0, 1, 3)[..., :self.v_dim].reshape(sq, b, self.nh_local * self.v_dim)
             out, bias = self.linear_proj(ctx)
         return out, bias
+
+
+class LatentSelfAttention(MegatronModule):
+    """Latent attention without a positional sub-head, whose cached latent can be shared between layers.
+
+    ``c_q = norm(W_dq h)``, ``q = W_uq c_q``; ``c = norm(W_dkv h)`` is the only thing cached; per head ``k = W_uk c``,
+    ``v = W_uv c``, ``score = q . k * scale``, causal softmax, ``W_o`` on the concatenated heads.  A layer built with
+    ``kv_source_layer = j`` owns no ``W_dkv``: it attends over the latents layer ``j`` produced (read from the paged
+    cache of the inference context, or from ``cross_layer`` in a whole-sequence forward) through its own ``W_uk / W_uv``.
+
+    Decoding and chunked prefill never expand the cache into keys and values: the query is carried into the latent
+    space (``q_lat = W_uk,h^T q_h``), one paged kernel computes ``softmax(q_lat . c * scale)`` and the weighted sum of
+    latents for all heads of a token (each cached row is read once), and ``W_uv,h`` is applied to that sum.
+    Tensor parallel: heads are split (``W_uq / W_uk / W_uv`` column-parallel, ``W_o`` row-parallel), the latents are
+    replicated."""
+
+    def __init__(self, config, layer_number: int, num_heads: int, qk_dim: int, v_dim: int, kv_rank: int, q_rank: int,
+                 softmax_scale: float, kv_source_layer: Optional[int] = None, eps: Optional[float] = None):
+        super().__init__(config)
+        from ..parallel.tp_layers import ColumnParallelLinear, RowParallelLinear
+        from .norms import FusedLayerNorm
+
+        self.layer_number, self.kv_source_layer = layer_number, kv_source_layer
+        tp = ps.get_tensor_model_parallel_world_size()
+        if num_heads % tp:
+            raise ValueError(f"latent attention: heads ({num_heads}) must divide by tp ({tp})")
+        self.nh, self.nh_local = num_heads, num_heads // tp
+        self.qk_dim, self.v_dim, self.kv_rank, self.q_rank = qk_dim, v_dim, kv_rank, q_rank
+        self.softmax_scale = float(softmax_scale)
+        eps = config.layernorm_epsilon if eps is None else eps
+        col = dict(config=config, init_method=config.init_method, bias=False, skip_bias_add=False)
+        self.linear_q_down_proj = ColumnParallelLinear(config.hidden_size, q_rank, gather_output=True, **col)
+        self.q_layernorm = FusedLayerNorm(config, q_rank, eps, normalization="RMSNorm")
+        self.q_layernorm.normalization = "RMSNorm"
+        self.linear_q_up_proj = ColumnParallelLinear(q_rank, num_heads * qk_dim, gather_output=False, **col)
+        if kv_source_layer is None:
+            self.linear_kv_down_proj = ColumnParallelLinear(config.hidden_size, kv_rank, gather_output=True, **col)
+            self.kv_layernorm = FusedLayerNorm(config, kv_rank, eps, normalization="RMSNorm")
+            self.kv_layernorm.normalization = "RMSNorm"
+        else:
+            self.linear_kv_down_proj = self.kv_layernorm = None
+        self.linear_k_up_proj = ColumnParallelLinear(kv_rank, num_heads * qk_dim, gather_output=False, **col)
+        self.linear_v_up_proj = ColumnParallelLinear(kv_rank, num_heads * v_dim, gather_output=False, **col)
+        for m in (self.linear_q_up_proj, self.linear_k_up_proj, self.linear_v_up_proj):
+            m.sequence_parallel = False
+            m.allreduce_dgrad = tp > 1
+        self.linear_proj = RowParallelLinear(num_heads * v_dim, config.hidden_size, config=config,
+                                             init_method=config.output_layer_init_method, bias=False,
+                                             input_is_parallel=True, skip_bias_add=True)
+
+    @property
+    def cache_layer(self) -> int:
+        """The layer whose latents this layer attends over."""
+        return self.layer_number if self.kv_source_layer is None else self.kv_source_layer
+
+    def forward(self, hidden_states, attention_mask=None, inference_context=None, cross_layer=None, **_):
+        s, b = hidden_states.shape[0], hidden_states.shape[1]
+        qc, _ = self.linear_q_down_proj(hidden_states)
+        q, _ = self.linear_q_up_proj(self.q_layernorm(qc))
+        q = q.view(s, b, self.nh_local, self.qk_dim)
+        c = None
+        if self.linear_kv_down_proj is not None:
+            kvc, _ = self.linear_kv_down_proj(hidden_states)
+            c = self.kv_layernorm(kvc)                                      # [s, b, r]
+        if inference_context is not None and not inference_context.is_static_batching():
+            # packed tokens [T, 1, ...] against the paged latent cache
+            wk = self.linear_k_up_proj.weight.view(self.nh_local, self.qk_dim, self.kv_rank)
+            wv = self.linear_v_up_proj.weight.view(self.nh_local, self.v_dim, self.kv_rank)
+            q_lat = torch.einsum("thd,hdr->thr", q[:, 0], wk)
+            o_lat = inference_context.attend_latent(self.cache_layer, q_lat, None if c is None else c[:, 0],
+                                                    self.softmax_scale)
+            ctx = torch.einsum("thr,hvr->thv", o_lat.to(wv.dtype), wv).reshape(s, 1, self.nh_local * self.v_dim)
+            return self.linear_proj(ctx)
+        if inference_context is not None:
+            raise NotImplementedError("latent attention serves through the dynamic (paged) engine")
+        if cross_layer is None:
+            cross_layer = {}
+        if c is not None:
+            cross_layer[self.layer_number] = c
+        c = cross_layer[self.cache_layer]
+        k, _ = self.linear_k_up_proj(c)
+        v, _ = self.linear_v_up_proj(c)
+        k = k.view(s, b, self.nh_local, self.qk_dim)
+        v = v.view(s, b, self.nh_local, self.v_dim)
+        width = max(self.qk_dim, self.v_dim)
+        pad = torch.nn.functional.pad
+        qp, kp = (pad(t, (0, width - self.qk_dim)) if width > self.qk_dim else t for t in (q, k))
+        vp = pad(v, (0, width - self.v_dim)) if width > self.v_dim else v
+        o = ops.attention(qp.permute(1, 2, 0, 3), kp.permute(1, 2, 0, 3), vp.permute(1, 2, 0, 3), self.softmax_scale,
+                          True, 0.0, self.training, None)
+        ctx = o.permute(2, 0, 1, 3)[..., :self.v_dim].reshape(s, b, self.nh_local * self.v_dim)
+        return self.linear_proj(ctx)

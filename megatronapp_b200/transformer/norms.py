@@ -66,3 +66,27 @@ class IdentityOp(nn.Module):
 class IdentityFuncOp(IdentityOp):
     def forward(self, *a, **k):
         return super().forward
+
+
+class ResidualRMSNorm(nn.Module):
+    """RMS norm of an fp32 residual stream, fused with the addition that precedes it: ``forward(x, delta)`` adds
+    ``delta`` (any dtype) into the fp32 ``x`` in place and returns ``(x, x / sqrt(mean(x^2) + eps) * weight)`` with the
+    normalised copy in ``out_dtype`` (the dtype the following projections run in)."""
+
+    def __init__(self, config, hidden_size: int, eps: float = 1e-5, out_dtype=None):
+        super().__init__()
+        self.eps, self.hidden_size = eps, hidden_size
+        dtype = config.params_dtype if config is not None else torch.float32
+        self.out_dtype = out_dtype or dtype
+        dev = "cpu" if (config is None or config.use_cpu_initialization or not torch.cuda.is_available()) \
+            else torch.cuda.current_device()
+        self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=dev))
+        setattr(self.weight, "sequence_parallel", bool(config.sequence_parallel) if config is not None else False)
+
+    def forward(self, x, delta=None):
+        from ..ops import seqmix
+
+        shape = x.shape
+        x2, y = seqmix.add_rms_norm(x.view(-1, shape[-1]), None if delta is None else delta.reshape(-1, shape[-1]),
+                                    self.weight, self.eps, self.out_dtype)
+        return x2.view(shape), y.view(shape)
