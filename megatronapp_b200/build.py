@@ -3,7 +3,9 @@
 ``build_all()`` compiles every ``csrc/*.cu`` with
 ``nvcc -gencode arch=compute_100a,code=sm_100a -lineinfo`` (cross-compiles without a GPU),
 the torch bindings with g++, links ``megatronapp_b200/_C.so`` and builds the pure-C++ dataset
-helpers ``megatronapp_b200/data/_helpers.so``.  Objects are cached by content hash (not mtime)
+helpers ``megatronapp_b200/data/_helpers.so``.  ``build_seq()`` builds the sequence-mixing kernels
+(``csrc/seqmix``) into ``megatronapp_b200/_C_seq.so``, an extension of its own, so that a model which only needs
+those (fp32 serving of a hybrid model, say) compiles nothing else on first use; ``build_all()`` includes it.  Objects are cached by content hash (not mtime)
 so the snapshot that travels to a GPU box never rebuilds.
 """
 from __future__ import annotations
@@ -61,8 +63,62 @@ def _torch_flags():
     return inc, libdir, abi
 
 
+# exact arithmetic for the recurrent scans and norms: no --use_fast_math here
+SEQ_NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "-diag-suppress", "177", "--expt-relaxed-constexpr"]
+
+
+def build_seq(verbose: bool = False, force: bool = False) -> Path:
+    """``csrc/seqmix/*.cu`` + ``bindings_seq.cpp`` -> ``_C_seq.so`` (content-hashed like the main extension)."""
+    BUILD.mkdir(exist_ok=True)
+    src_dir = CSRC / "seqmix"
+    headers = sorted(src_dir.glob("*.h")) + sorted(src_dir.glob("*.cuh"))
+    stamp_path = BUILD / "stamps_seq.json"
+    stamps = json.loads(stamp_path.read_text()) if stamp_path.exists() else {}
+    nvcc = _nvcc()
+    cuda_home = str(Path(nvcc).resolve().parent.parent)
+    inc, libdir, abi = _torch_flags()
+    jobs, objs = [], []
+    for src in sorted(src_dir.glob("*.cu")):
+        obj = BUILD / ("seq_" + src.stem + ".o")
+        objs.append(obj)
+        key = _hash_files([src] + headers, " ".join(SEQ_NVCC_FLAGS + ARCH_FLAGS))
+        if force or not obj.exists() or stamps.get(obj.name) != key:
+            jobs.append((obj.name, key, [nvcc, *ARCH_FLAGS, *SEQ_NVCC_FLAGS, "-c", str(src), "-o", str(obj)]))
+    bsrc, bobj = src_dir / "bindings_seq.cpp", BUILD / "seq_bindings.o"
+    objs.append(bobj)
+    cxx_flags = ["-O2", "-std=c++17", "-fPIC", f"-D_GLIBCXX_USE_CXX11_ABI={abi}", "-DTORCH_EXTENSION_NAME=_C_seq",
+                 "-DTORCH_API_INCLUDE_EXTENSION_H", "-I", cuda_home + "/include", *inc, "-w"]
+    bkey = _hash_files([bsrc] + headers, " ".join(cxx_flags))
+    if force or not bobj.exists() or stamps.get(bobj.name) != bkey:
+        jobs.append((bobj.name, bkey, ["g++", *cxx_flags, "-c", str(bsrc), "-o", str(bobj)]))
+
+    def _do(job):
+        name, key, cmd = job
+        if verbose:
+            print("[b200 build]", name, flush=True)
+        _run(cmd)
+        return name, key
+
+    if jobs:
+        with ThreadPoolExecutor(max_workers=min(8, len(jobs))) as ex:
+            for name, key in ex.map(_do, jobs):
+                stamps[name] = key
+    so = PKG / "_C_seq.so"
+    link_key = hashlib.sha256("".join(stamps.get(o.name, "") for o in objs).encode()).hexdigest()[:20]
+    if force or jobs or not so.exists() or stamps.get("_C_seq.so") != link_key:
+        tmp = PKG / f"_C_seq.so.{os.getpid()}.tmp"          # link aside, then rename: concurrent first calls never see half a file
+        _run(["g++", "-shared", "-o", str(tmp), *map(str, objs), f"-L{libdir}", f"-L{cuda_home}/lib64", "-lc10", "-lc10_cuda",
+              "-ltorch_cpu", "-ltorch_cuda", "-ltorch", "-ltorch_python", "-lcudart", f"-Wl,-rpath,{libdir}",
+              f"-Wl,-rpath,{cuda_home}/lib64"])
+        os.replace(tmp, so)
+        stamps["_C_seq.so"] = link_key
+    stamp_path.write_text(json.dumps(stamps, indent=1))
+    return so
+
+
 def build_all(verbose: bool = False, force: bool = False) -> Path:
     BUILD.mkdir(exist_ok=True)
+    build_seq(verbose, force)
     headers = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh"))
     cu_sources = sorted(CSRC.glob("*.cu")) + [p for p in sorted(CSRC.glob("*.cpp")) if p.name != "bindings.cpp"]
     stamp_path = BUILD / "stamps.json"

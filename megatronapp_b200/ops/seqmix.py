@@ -67,6 +67,11 @@ def _host(x) -> List[int]:
     return x.tolist() if torch.is_tensor(x) else list(x)
 
 
+def _rows3(t: torch.Tensor) -> torch.Tensor:
+    """``[T, heads, dim]`` as the kernels take it: contiguous heads, any row stride (a column slice of a fused projection)."""
+    return t if (t.stride(2) == 1 and t.stride(1) == t.shape[2]) else t.contiguous()
+
+
 class PackedBatch:
     """Sequence boundaries and state rows of one packed step, on the host and on the device."""
 
@@ -75,6 +80,9 @@ class PackedBatch:
         self.cu = _i32(self.cu_host, device)
         self.slots = _i32(self.slots_host, device)
         self.num_seqs = len(self.slots_host)
+        # the sequence of every packed token (the convolution kernel is token-parallel)
+        self.tok_seq = _i32([r for r in range(len(self.slots_host)) for _ in range(self.cu_host[r + 1] - self.cu_host[r])], device) \
+            if str(device) != "cpu" else None
         self.max_len = max((b - a for a, b in zip(self.cu_host[:-1], self.cu_host[1:])), default=0)
 
     @classmethod
@@ -131,8 +139,9 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, win
     of this step (zeros at a sequence's start); on return it holds the last ``taps - 1`` inputs seen."""
     if x.is_cuda:
         kernel_calls["causal_conv_silu"] += 1
-        y = torch.empty_like(x)
-        ext().causal_conv_silu(x.contiguous(), weight.contiguous(), pb.cu, pb.slots, window, y)
+        y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+        ext().causal_conv_silu(x if x.stride(1) == 1 else x.contiguous(), weight.contiguous(), pb.cu, pb.slots, pb.tok_seq,
+                               window, y)
         return y
     taps = weight.shape[1]
     w = weight.float()
@@ -168,7 +177,7 @@ def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay
     if q.is_cuda:
         kernel_calls["delta_rule_scan"] += 1
         o = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
-        ext().delta_rule_scan(q.contiguous(), k.contiguous(), v.contiguous(), log_decay.contiguous(), beta.contiguous(),
+        ext().delta_rule_scan(_rows3(q), _rows3(k), _rows3(v), log_decay.contiguous(), beta.contiguous(),
                               pb.cu, pb.slots, state, o, -1.0 if unit_eps is None else float(unit_eps), float(q_scale))
         return o
     qf, kf, vf = q.float(), k.float(), v.float()
@@ -210,7 +219,7 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_i: torch.T
     if q.is_cuda:
         kernel_calls["mlstm_scan"] += 1
         o = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
-        ext().mlstm_scan(q.contiguous(), k.contiguous(), v.contiguous(), log_i.contiguous(), log_f.contiguous(),
+        ext().mlstm_scan(_rows3(q), _rows3(k), _rows3(v), log_i.contiguous(), log_f.contiguous(),
                          pb.cu, pb.slots, state, norm_state, max_state, o, float(q_scale), float(denom_eps))
         return o
     qf, kf, vf = q.float() * q_scale, k.float(), v.float()

@@ -58,12 +58,19 @@ def latent_attention(h, c, W, pre, mx, eps):
     q = (rms_norm(h @ W[pre + "dq"].T, W[pre + "dq.norm"], eps) @ W[pre + "uq"].T).view(T, H, d)
     k = (c @ W[pre + "uk"].T).view(T, H, d)
     v = (c @ W[pre + "uv"].T).view(T, H, dv)
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
+    out = causal_attention_loop(q, k, v, mx["scale"])
+    return out.reshape(T, H * dv) @ W[pre + "o"].T
+
+
+def causal_attention_loop(q, k, v, scale):
+    """q, k [T, H, d], v [T, H, dv] -> [T, H, dv]; position i sees every j <= i."""
+    T, H = q.shape[0], q.shape[1]
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
     for i in range(T):
         for a in range(H):
-            s = (k[:i + 1, a] @ q[i, a]) * mx["scale"]
+            s = (k[:i + 1, a] @ q[i, a]) * scale
             out[i, a] = torch.softmax(s, 0) @ v[:i + 1, a]
-    return out.reshape(T, H * dv) @ W[pre + "o"].T
+    return out
 
 
 def short_conv_silu(x, w):
@@ -89,17 +96,25 @@ def channel_delta(h, W, pre, mx, eps):
     dt = torch.nn.functional.softplus((h @ W[pre + "a1"].T) @ W[pre + "a2"].T + W[pre + "dt_bias"]).view(T, H, d)
     g = torch.exp(-torch.exp(W[pre + "A_log"]).view(1, H, 1) * dt)                       # [T, H, d]
     gate = torch.sigmoid((h @ W[pre + "g1"].T) @ W[pre + "g2"].T).view(T, H, dv)
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
+    out = delta_rule_loop(q, k, v, g, beta)
+    out = out / torch.sqrt((out * out).mean(-1, keepdim=True) + eps) * W[pre + "norm"] * gate
+    return out.reshape(T, H * dv) @ W[pre + "o"].T
+
+
+def delta_rule_loop(q, k, v, g, beta):
+    """q, k [T, KH, d] (already unit length / scaled), v [T, H, dv], decay g [T, H, d], beta [T, H] -> o [T, H, dv]."""
+    T, H, dv = v.shape
+    KH, d = q.shape[1], q.shape[2]
+    out = torch.zeros(T, H, dv, dtype=q.dtype)
     for a in range(H):
         kh = a // (H // KH)
-        S = torch.zeros(d, dv, dtype=h.dtype)
+        S = torch.zeros(d, dv, dtype=q.dtype)
         for t in range(T):
             S = g[t, a].unsqueeze(1) * S
             u = beta[t, a] * (v[t, a] - S.T @ k[t, kh])
             S = S + torch.outer(k[t, kh], u)
             out[t, a] = S.T @ q[t, kh]
-    out = out / torch.sqrt((out * out).mean(-1, keepdim=True) + eps) * W[pre + "norm"] * gate
-    return out.reshape(T, H * dv) @ W[pre + "o"].T
+    return out
 
 
 def mlstm(h, W, pre, mx, eps):
@@ -109,11 +124,21 @@ def mlstm(h, W, pre, mx, eps):
     v = (h @ W[pre + "v"].T).view(T, H, dv)
     ig = cap * torch.tanh((h @ W[pre + "i"].T + W[pre + "i.b"]) / cap)                   # [T, H]
     fg = torch.nn.functional.logsigmoid(cap * torch.tanh((h @ W[pre + "f"].T + W[pre + "f.b"]) / cap))
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
+    out = mlstm_loop(q, k, v, ig, fg)
+    out = out / torch.sqrt((out * out).mean(-1, keepdim=True) + eps)
+    out = out.reshape(T, H * dv) * W[pre + "norm"] * torch.sigmoid(h @ W[pre + "g"].T)
+    return out @ W[pre + "o"].T
+
+
+def mlstm_loop(q, k, v, ig, fg):
+    """q (scaled), k [T, H, d], v [T, H, dv], log gates ig, fg [T, H] -> o [T, H, dv]."""
+    T, H, dv = v.shape
+    d = q.shape[2]
+    out = torch.zeros(T, H, dv, dtype=q.dtype)
     for a in range(H):
-        S = torch.zeros(d, dv, dtype=h.dtype)
-        n = torch.zeros(d, dtype=h.dtype)
-        m = torch.zeros((), dtype=h.dtype)
+        S = torch.zeros(d, dv, dtype=q.dtype)
+        n = torch.zeros(d, dtype=q.dtype)
+        m = torch.zeros((), dtype=q.dtype)
         for t in range(T):
             m_new = torch.maximum(fg[t, a] + m, ig[t, a])
             keep, put = torch.exp(fg[t, a] + m - m_new), torch.exp(ig[t, a] - m_new)
@@ -121,9 +146,7 @@ def mlstm(h, W, pre, mx, eps):
             n = keep * n + put * k[t, a]
             m = m_new
             out[t, a] = S.T @ q[t, a] / (torch.maximum((n @ q[t, a]).abs(), torch.exp(-m)) + 1e-6)
-    out = out / torch.sqrt((out * out).mean(-1, keepdim=True) + eps)
-    out = out.reshape(T, H * dv) * W[pre + "norm"] * torch.sigmoid(h @ W[pre + "g"].T)
-    return out @ W[pre + "o"].T
+    return out
 
 
 def forward(config, weights, tokens, dtype=torch.float64, return_layers=False):
@@ -158,8 +181,9 @@ def forward(config, weights, tokens, dtype=torch.float64, return_layers=False):
     return (logits, torch.stack(layers)) if return_layers else logits
 
 
-def random_weights(config, seed=0, dtype=torch.float32):
-    """Random tensors with the checkpoint's names and shapes for ``config`` (gains near 1, small projections)."""
+def random_weights(config, seed=0, dtype=torch.float32, low_rank=8):
+    """Random tensors with the checkpoint's names and shapes for ``config`` (gains near 1, small projections);
+    ``low_rank`` is the inner width of the decay and gate projections of channel_delta layers."""
     g = torch.Generator().manual_seed(seed)
     width, W = config["width"], {}
 
@@ -181,7 +205,7 @@ def random_weights(config, seed=0, dtype=torch.float32):
             lin(p + "uk", H * d, r), lin(p + "uv", H * dv, r), lin(p + "o", width, H * dv)
         elif layer["type"] == "channel_delta":
             H, KH, d, dv, taps = mx["heads"], mx["kv_heads"], mx["dim"], mx["vdim"], mx["conv"]
-            lo = mx.get("low_rank", 8)
+            lo = low_rank
             for nm, n in (("q", KH * d), ("k", KH * d), ("v", H * dv)):
                 lin(p + nm, n, width)
                 W[p + nm + ".conv"] = (torch.randn(n, taps, generator=g) * 0.5).to(dtype)
