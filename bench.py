@@ -437,7 +437,16 @@ def main():
     ap.add_argument("--trace-scopes", action="store_true", help="(kept for compatibility; scopes are always reported)")
     ap.add_argument("--no-fused-rs", action="store_true", help="GEMM + NCCL reduce-scatter instead of the fused GEMM->RS kernel")
     ap.add_argument("--fused-rs", action="store_true", help="(default now) fuse GEMM->reduce-scatter")
+    ap.add_argument("--serving", action="store_true",
+                    help="instead of the training step: prefill / decode throughput of the hybrid (Zikunex) design beside the closest "
+                         "existing model through the dynamic engine, and its kernels against their rooflines (1 GPU)")
+    ap.add_argument("--serving-size", default="medium", choices=["small", "medium"])
     args = ap.parse_args()
+    if args.serving:
+        from megatronapp_b200.bench_serving import run as run_serving
+
+        run_serving(args)
+        return
     if args.no_fused_rs:
         os.environ["B200_FUSED_RS"] = "0"
     if args.impl == "reference":

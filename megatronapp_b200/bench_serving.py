@@ -1,0 +1,281 @@
+"""Serving benchmark of the hybrid (Zikunex) design beside the closest existing model, a GPT decoder with grouped-query
+attention and the same feed-forwards, both through ``DynamicInferenceEngine.forward_tokens`` (``bench.py --serving``).
+
+Two parts, random weights, bf16:
+
+* model level: prefill (a few long prompts in one step) and decode (many requests, one token each, against a filled
+  cache) in tokens/s, for both models at equal width, depth, head count and feed-forward sizes;
+* kernel level: every kernel of the new design alone, with its achieved fraction of the roofline (measured copy
+  bandwidth for the memory-bound ones, fp32 FMA rate for the sequential scans' prefill), next to the like kernel of the
+  existing models (paged GQA attention, the fused LayerNorm/RMSNorm kernel, the Mamba SSD scan).
+
+Timing: CUDA events on the launching stream, warm-up first, an L2-sized buffer rewritten between timed kernel launches.
+"""
+from __future__ import annotations
+
+import json
+import os
+import time
+
+import torch
+
+SIZES = {
+    # width, layers, heads, head dim, latent ranks (kv, q), dense ff, experts, expert ff, top, shared ff, vocab
+    "small": dict(width=1024, layers=4, heads=8, dim=128, kv_rank=256, q_rank=384, ff=4096, experts=8, expert_ff=512, top=2,
+                  shared_ff=1024, vocab=32000),
+    "medium": dict(width=2048, layers=8, heads=16, dim=128, kv_rank=512, q_rank=768, ff=8192, experts=16, expert_ff=1024, top=4,
+                   shared_ff=2048, vocab=32000),
+}
+
+
+def _peaks():
+    p = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        with open(p) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+def zikunex_config(s):
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]},
+           "router": {"experts": s["experts"], "top": s["top"], "groups": {"count": 4, "keep": 2}}, "shared": {"ff": s["shared_ff"]}}
+    dense = {"kind": "dense", "ff": s["ff"]}
+    lat = {"heads": s["heads"], "dim": s["dim"], "vdim": s["dim"], "kv_rank": s["kv_rank"], "q_rank": s["q_rank"],
+           "scale": s["dim"] ** -0.5}
+    pattern = [("mlstm", {"heads": s["heads"], "dim": s["dim"], "vdim": s["dim"], "gate_cap": 15.0}, dense),
+               ("latent_attention", lat, moe),
+               ("channel_delta", {"heads": s["heads"], "kv_heads": s["heads"] // 2, "dim": s["dim"], "vdim": s["dim"], "conv": 4,
+                                  "decay_rank": 64, "gate_rank": 64}, moe),
+               ("latent_attention", dict(lat, kv_from=1), moe)]
+    layers = []
+    for i in range(s["layers"]):
+        t, mx, mlp = pattern[i % 4]
+        mx = dict(mx)
+        if "kv_from" in mx:
+            mx["kv_from"] = i - 2
+        layers.append({"type": t, "mixer": mx, "mlp": mlp})
+    return {"architecture": "Zikunex", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5}, "embedding": {"scale": 1.0},
+            "layers": layers}
+
+
+def build_zikunex(s, device):
+    from .models.zikunex import ZikunexConfig, ZikunexModel
+    from .parallel import state as ps
+
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_model_parallel(1, 1)
+    zcfg = ZikunexConfig.from_dict(zikunex_config(s))
+    base = zcfg.base_transformer_config(torch.bfloat16, use_cpu_initialization=False)
+    return ZikunexModel(zcfg, base).to(device).eval()
+
+
+def build_gpt(s, device):
+    """The closest existing model: GQA attention with rotary positions, RMSNorm, the same MoE / dense feed-forward sizes
+    (3 of 4 layers MoE, like the hybrid), squared-ReLU experts, a shared expert."""
+    from .config.transformer_config import TransformerConfig
+    from .models.gpt.gpt_layer_specs import get_gpt_decoder_block_spec
+    from .models.gpt.gpt_model import GPTModel
+    from .parallel import state as ps
+    from .transformer.mlp import squared_relu
+
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_model_parallel(1, 1)
+    cfg = TransformerConfig(num_layers=s["layers"], hidden_size=s["width"], num_attention_heads=s["heads"], kv_channels=s["dim"],
+                            num_query_groups=max(1, s["heads"] // 4), ffn_hidden_size=s["ff"], normalization="RMSNorm",
+                            add_bias_linear=False, activation_func=squared_relu, hidden_dropout=0.0, attention_dropout=0.0,
+                            params_dtype=torch.bfloat16, bf16=True, num_moe_experts=s["experts"], moe_router_topk=s["top"],
+                            moe_ffn_hidden_size=s["expert_ff"], moe_shared_expert_intermediate_size=s["shared_ff"],
+                            moe_grouped_gemm=True, moe_token_dispatcher_type="allgather", moe_router_load_balancing_type="none",
+                            moe_layer_freq=[0 if i % 4 == 0 else 1 for i in range(s["layers"])], bias_activation_fusion=False)
+    model = GPTModel(cfg, get_gpt_decoder_block_spec(cfg, use_transformer_engine=False), s["vocab"], 8192,
+                     position_embedding_type="rope", parallel_output=False)
+    return model.to(device).eval()
+
+
+def _engine(model, max_tokens, max_requests):
+    from .data.tokenizer import NullTokenizer
+    from .inference import DynamicInferenceEngine
+
+    bs = 16
+    return DynamicInferenceEngine(model, NullTokenizer(1000), max_sequence_length=8192, num_blocks=max_tokens // bs + max_requests,
+                                  block_size=bs, max_tokens_per_step=max_tokens, max_requests=max_requests)
+
+
+def _timed(fn, steps, warmup):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(steps):
+        fn()
+    b.record()
+    torch.cuda.synchronize()
+    return a.elapsed_time(b) / steps
+
+
+def serve_numbers(model, vocab, prompts, prompt_len, decoders, context, steps, warmup):
+    """(prefill tokens/s, decode tokens/s) through the engine's forward."""
+    g = torch.Generator().manual_seed(0)
+    eng = _engine(model, max(prompts * prompt_len, decoders * (context + steps + warmup + 2)) + 64, max(prompts, decoders))
+    ctx = eng.context
+    n = [0]
+
+    def prefill():
+        ids = [f"p{n[0]}_{i}" for i in range(prompts)]
+        n[0] += 1
+        for r in ids:
+            ctx.add_request(r)
+        eng.forward_tokens([(r, torch.randint(0, vocab, (prompt_len,), generator=g).tolist()) for r in ids])
+        for r in ids:
+            ctx.release(r)
+
+    ms_prefill = _timed(prefill, steps, warmup)
+    ids = [f"d{i}" for i in range(decoders)]
+    for r in ids:
+        ctx.add_request(r)
+    for lo in range(0, decoders, 8):                 # fill the caches
+        eng.forward_tokens([(r, torch.randint(0, vocab, (context,), generator=g).tolist()) for r in ids[lo:lo + 8]])
+    tok = torch.randint(0, vocab, (decoders,), generator=g).tolist()
+    ms_decode = _timed(lambda: eng.forward_tokens([(r, [t]) for r, t in zip(ids, tok)]), steps, warmup)
+    for r in ids:
+        ctx.release(r)
+    return prompts * prompt_len / ms_prefill * 1e3, decoders / ms_decode * 1e3, ms_prefill, ms_decode
+
+
+def kernel_numbers(s, device):
+    """Every new kernel alone and its like kernel: time, achieved bytes/s (or flop/s) and the fraction of the roofline."""
+    from . import ops
+    from .ops import seqmix
+
+    hbm, how = _peaks()
+    fma_peak = 148 * 128 * 2 * 1.965e9 / 1e12        # fp32 TFLOP/s of the CUDA cores at the maximum clock
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=device)
+    out = {}
+
+    def bench(name, fn, nbytes, flops=0.0, like=None):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(5):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ms = sorted(ts)[len(ts) // 2]
+        gbs = nbytes / ms / 1e6
+        tfl = flops / ms / 1e9
+        frac = max(gbs / hbm, tfl / fma_peak if flops else 0.0)
+        out[name] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "TFLOP/s": round(tfl, 2), "roofline_frac": round(frac, 3),
+                     "bound": "fma" if flops and tfl / fma_peak > gbs / hbm else "hbm", "like": like}
+
+    H, d, r, W = s["heads"], s["dim"], s["kv_rank"], s["width"]
+    bf = torch.bfloat16
+    # -- decode attention: 64 requests x 2048 cached tokens
+    R, L, bs = 64, 2048, 16
+    nblk = R * L // bs
+    table = torch.randperm(nblk, device=device).to(torch.int32).view(R, L // bs)
+    req = torch.arange(R, dtype=torch.int32, device=device)
+    lens = torch.full((R,), L, dtype=torch.int32, device=device)
+    cache = torch.randn(nblk * bs, r, device=device, dtype=bf)
+    q_lat = torch.randn(R, H, r, device=device, dtype=bf)
+    bench("latent_attention_paged.decode", lambda: seqmix.latent_attention_paged(q_lat, cache, table, req, lens, bs, 0.05),
+          R * L * r * 2, like="paged_attention.decode")
+    ng = max(1, H // 4)
+    kc = torch.randn(nblk * bs, ng, d, device=device, dtype=bf)
+    vc = torch.randn(nblk * bs, ng, d, device=device, dtype=bf)
+    qg = torch.randn(R, H, d, device=device, dtype=bf)
+    if ops.ext().paged_attention_supported(d, H // ng):
+        bench("paged_attention.decode", lambda: ops.ext().paged_attention(qg, kc, vc, table, req, lens, bs, d ** -0.5, 1),
+              R * L * ng * d * 2 * 2)
+    # -- prefill attention: one prompt of 2048 tokens
+    T = 2048
+    table1 = torch.randperm(T // bs, device=device).to(torch.int32).view(1, -1)
+    req1 = torch.zeros(T, dtype=torch.int32, device=device)
+    len1 = torch.arange(1, T + 1, dtype=torch.int32, device=device)
+    q1 = torch.randn(T, H, r, device=device, dtype=bf)
+    bench("latent_attention_paged.prefill", lambda: seqmix.latent_attention_paged(q1, cache, table1, req1, len1, bs, 0.05),
+          T * r * 2 + T * H * r * 6, flops=T * (T + 1) / 2 * H * r * 4, like="paged_attention.prefill")
+    qg1 = torch.randn(T, H, d, device=device, dtype=bf)
+    if ops.ext().paged_attention_supported(d, H // ng):
+        bench("paged_attention.prefill", lambda: ops.ext().paged_attention(qg1, kc, vc, table1, req1, len1, bs, d ** -0.5, 1),
+              T * ng * d * 4 + T * H * d * 4, flops=T * (T + 1) / 2 * H * d * 4)
+    # -- scans: decode (64 sequences x 1 token, state bound) and prefill (4 x 2048 tokens, FMA bound)
+    for tag, R_, n in (("decode", 64, 1), ("prefill", 4, 2048)):
+        T_ = R_ * n
+        pb = seqmix.PackedBatch([i * n for i in range(R_ + 1)], list(range(R_)), device)
+        q = torch.randn(T_, H, d, device=device, dtype=bf)
+        k = torch.randn(T_, H, d, device=device, dtype=bf)
+        v = torch.randn(T_, H, d, device=device, dtype=bf)
+        ld = -torch.rand(T_, H, d, device=device) * 0.1
+        beta = torch.rand(T_, H, device=device)
+        S = torch.zeros(R_, H, d, d, device=device)
+        state_bytes = R_ * H * d * d * 4 * 2
+        io = T_ * H * d * 2 * 3 + T_ * H * d * 4 * 2
+        bench(f"delta_rule_scan.{tag}", lambda: seqmix.delta_rule_scan(q, k, v, ld, beta, pb, S), state_bytes + io,
+              flops=T_ * H * d * d * 8, like="ssd_scan (PyTorch)")
+        li, lf = torch.randn(T_, H, device=device), -torch.rand(T_, H, device=device)
+        nS, mS = torch.zeros(R_, H, d, device=device), torch.zeros(R_, H, device=device)
+        bench(f"mlstm_scan.{tag}", lambda: seqmix.mlstm_scan(q, k, v, li, lf, pb, S, nS, mS, d ** -0.5), state_bytes + io,
+              flops=T_ * H * d * d * 4, like="ssd_scan (PyTorch)")
+        from .ssm.mamba import ssd_scan
+
+        x4 = v.view(R_, n, H, d)
+        dt = torch.rand(R_, n, H, device=device) * 0.1
+        A = -torch.rand(H, device=device)
+        B4, C4 = k.view(R_, n, H, d)[:, :, :1], q.view(R_, n, H, d)[:, :, :1]
+        Dp = torch.ones(H, device=device)
+        S0 = torch.zeros(R_, H, d, d, device=device)
+        bench(f"ssd_scan (PyTorch).{tag}", lambda: ssd_scan(x4, dt, A, B4, C4, Dp, 64, S0), state_bytes + io, flops=T_ * H * d * d * 4)
+    # -- norms and convolution over 8192 tokens
+    T = 8192
+    x = torch.randn(T, W, device=device)
+    delta = torch.randn(T, W, device=device, dtype=bf)
+    w = torch.ones(W, device=device, dtype=bf)
+    bench("add_rms_norm", lambda: seqmix.add_rms_norm(x, delta, w, 1e-5, bf), T * W * (4 + 4 + 2 + 2), like="layer_norm (rms)")
+    xb = torch.randn(T, W, device=device, dtype=bf)
+    bench("layer_norm (rms)", lambda: ops.layer_norm(xb, w, None, 1e-5, rms=True), T * W * 4)
+    o = torch.randn(T, H, d, device=device)
+    gate = torch.randn(T, H * d, device=device, dtype=bf)
+    wn = torch.ones(d, device=device, dtype=bf)
+    bench("gated_head_rms_norm", lambda: seqmix.gated_head_rms_norm(o, wn, gate, 1e-5, bf), T * H * d * (4 + 2 + 2), like="layer_norm (rms)")
+    C = 3 * H * d
+    xc = torch.randn(T, C, device=device, dtype=bf)
+    wc = torch.randn(C, 4, device=device, dtype=bf)
+    pbc = seqmix.PackedBatch([0, T], [0], device)
+    win = torch.zeros(1, 3, C, device=device, dtype=bf)
+    bench("causal_conv_silu", lambda: seqmix.causal_conv_silu(xc, wc, pbc, win), T * C * 4, like="layer_norm (rms)")
+    lg = torch.randn(T, s["experts"], device=device)
+    bench("group_limited_router", lambda: seqmix.group_limited_router(lg, s["top"], 4, 2), T * s["experts"] * 9, like="router_topk")
+    from .ops.moe import router_topk
+
+    bench("router_topk", lambda: router_topk(lg, s["top"], True, None), T * s["experts"] * 9)
+    return out, {"hbm_gbs": hbm, "fp32_fma_tflops": round(fma_peak, 1), "peaks": how}
+
+
+def run(args):
+    assert torch.cuda.is_available(), "--serving needs a GPU"
+    dev = "cuda:0"
+    torch.cuda.set_device(0)
+    s = SIZES[args.serving_size]
+    res = {"metric": "serving_tokens_per_s", "size": args.serving_size, "dtype": "bf16", "data": "synthetic", "steps": args.steps,
+           "warmup": max(3, args.warmup), "config": dict(s, prompts=4, prompt_len=2048, decoders=32, context=1024,
+                                                        l2="model steps read weights and caches larger than L2; kernel "
+                                                           "timings rewrite a 160 MB buffer between launches")}
+    with torch.no_grad():
+        for name, build in (("zikunex", build_zikunex), ("gpt_gqa_moe", build_gpt)):
+            t0 = time.time()
+            model = build(s, dev)
+            pre, dec, ms_p, ms_d = serve_numbers(model, s["vocab"], 4, 2048, 32, 1024, args.steps, max(3, args.warmup))
+            res[name] = {"prefill_tokens_per_s": round(pre, 1), "decode_tokens_per_s": round(dec, 1), "prefill_ms": round(ms_p, 2),
+                         "decode_ms": round(ms_d, 2), "params_M": round(sum(p.numel() for p in model.parameters()) / 1e6, 1),
+                         "build_s": round(time.time() - t0, 1)}
+            del model
+            torch.cuda.empty_cache()
+        res["kernels"], res["roofline"] = kernel_numbers(s, dev)
+    print(json.dumps(res), flush=True)
+    return res

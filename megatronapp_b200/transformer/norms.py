@@ -77,7 +77,7 @@ class ResidualRMSNorm(nn.Module):
         super().__init__()
         self.eps, self.hidden_size = eps, hidden_size
         dtype = config.params_dtype if config is not None else torch.float32
-        self.out_dtype = out_dtype or dtype
+        self.out_dtype = out_dtype          # None: the weight's dtype at call time
         dev = "cpu" if (config is None or config.use_cpu_initialization or not torch.cuda.is_available()) \
             else torch.cuda.current_device()
         self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=dev))
@@ -88,5 +88,5 @@ class ResidualRMSNorm(nn.Module):
 
         shape = x.shape
         x2, y = seqmix.add_rms_norm(x.view(-1, shape[-1]), None if delta is None else delta.reshape(-1, shape[-1]),
-                                    self.weight, self.eps, self.out_dtype)
+                                    self.weight, self.eps, self.out_dtype or self.weight.dtype)
         return x2.view(shape), y.view(shape)

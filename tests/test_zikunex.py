@@ -192,15 +192,19 @@ def test_greedy_generation_through_the_engine(device):
 
 @pytest.mark.gpu
 def test_bfloat16_serving_stays_within_rounding():
-    model, W = build(HYBRID, "cuda", torch.bfloat16)
+    """bf16 projections around fp32 state, scores and residual.  A router's close call may flip an expert under bf16
+    rounding and move single positions, so the bound is on the typical position, with a loose one on all."""
+    cfg = config_of([layer(DELTA, {"kind": "dense", "ff": 96}), layer(LAT, MOE_A), layer(MLSTM), layer(LAT, MOE_A, kv_from=1),
+                     layer(DELTA_B, {"kind": "dense", "ff": 32})])
+    model, W = build(cfg, "cuda", torch.bfloat16)
     Wb = {k: v.to(torch.bfloat16).float() if v.is_floating_point() else v for k, v in W.items()}
     toks = tokens_of(60, seed=14)
-    want = oracle.forward(HYBRID, Wb, toks)
+    want = oracle.forward(cfg, Wb, toks)
     got = run_cut(replayer(model), "a", toks, [40, 5])
     d = got.double().cpu() - want
     d = d - d.mean(-1, keepdim=True)
-    rel = (d.pow(2).mean(-1).sqrt() / want.std(-1)).max().item()
-    assert rel < 0.05, rel
+    rel = d.pow(2).mean(-1).sqrt() / want.std(-1)
+    assert rel.median().item() < 0.03 and rel.max().item() < 0.5, (rel.median().item(), rel.max().item())
     assert seqmix.kernel_calls["delta_rule_scan"] and seqmix.kernel_calls["latent_attention_paged"]
 
 
@@ -320,7 +324,7 @@ def test_group_limited_router_keeps_the_best_groups_only(device):
     z = torch.full((3, E), -2.0)
     z[0, 0], z[0, 1], z[0, 2] = 3.0, 2.9, 2.8         # group 0 holds the three largest; group 2 the fourth
     z[0, 7] = 2.0
-    z[1, 11], z[1, 3], z[1, 4] = 1.0, 0.9, 0.8        # three groups compete for two places
+    z[1, 11], z[1, 3], z[1, 6], z[1, 10] = 1.0, 0.9, 0.8, -1.0      # three groups compete for two places: expert 6 loses to 10
     z[2] = torch.arange(E).float() * 0.1
     probs, rmap = seqmix.group_limited_router(z.to(device), 3, G, 2)
     s = torch.softmax(z.double(), -1)
@@ -328,8 +332,8 @@ def test_group_limited_router_keeps_the_best_groups_only(device):
         ids, w = oracle.route(z[t].double(), 3, G, 2)
         assert sorted(ids) == rmap[t].nonzero().flatten().tolist()
         close(probs[t, ids], w, 1e-6)
-    assert rmap[0].nonzero().flatten().tolist() == [0, 1, 2]                 # never expert 7 of the third-best group... kept 2
-    assert rmap[1].nonzero().flatten().tolist()[-1] == 11 and not bool(rmap[1, 4])
+    assert rmap[0].nonzero().flatten().tolist() == [0, 1, 2]
+    assert rmap[1].nonzero().flatten().tolist() == [3, 10, 11]
     raw, _ = seqmix.group_limited_router(z.to(device), 3, G, 2, renormalize=False)
     close(raw[0, [0, 1, 2]], s[0, [0, 1, 2]], 1e-6)
 
