@@ -183,22 +183,22 @@ def kernel_numbers(s, device):
     lens = torch.full((R,), L, dtype=torch.int32, device=device)
     cache = torch.randn(nblk * bs, r, device=device, dtype=bf)
     q_lat = torch.randn(R, H, r, device=device, dtype=bf)
-    bench("latent_attention_paged.decode", lambda: seqmix.latent_attention_paged(q_lat, cache, table, req, lens, bs, 0.05),
-          R * L * r * 2, like="paged_attention.decode")
+    bench("latent_attention_paged.decode", lambda: seqmix.latent_attention_paged(q_lat, cache, table, req, lens, bs, 0.05, L),
+          R * L * r * 2, flops=R * L * H * r * 4, like="paged_attention.decode")
     ng = max(1, H // 4)
     kc = torch.randn(nblk * bs, ng, d, device=device, dtype=bf)
     vc = torch.randn(nblk * bs, ng, d, device=device, dtype=bf)
     qg = torch.randn(R, H, d, device=device, dtype=bf)
     if ops.ext().paged_attention_supported(d, H // ng):
         bench("paged_attention.decode", lambda: ops.ext().paged_attention(qg, kc, vc, table, req, lens, bs, d ** -0.5, 1),
-              R * L * ng * d * 2 * 2)
+              R * L * ng * d * 2 * 2, flops=R * L * H * d * 4)
     # -- prefill attention: one prompt of 2048 tokens
     T = 2048
     table1 = torch.randperm(T // bs, device=device).to(torch.int32).view(1, -1)
     req1 = torch.zeros(T, dtype=torch.int32, device=device)
     len1 = torch.arange(1, T + 1, dtype=torch.int32, device=device)
     q1 = torch.randn(T, H, r, device=device, dtype=bf)
-    bench("latent_attention_paged.prefill", lambda: seqmix.latent_attention_paged(q1, cache, table1, req1, len1, bs, 0.05),
+    bench("latent_attention_paged.prefill", lambda: seqmix.latent_attention_paged(q1, cache, table1, req1, len1, bs, 0.05, T),
           T * r * 2 + T * H * r * 6, flops=T * (T + 1) / 2 * H * r * 4, like="paged_attention.prefill")
     qg1 = torch.randn(T, H, d, device=device, dtype=bf)
     if ops.ext().paged_attention_supported(d, H // ng):

@@ -1,5 +1,6 @@
 // PyTorch bindings of the sequence-mixing kernels (pybind11 module megatronapp_b200._C_seq).
 #include <torch/extension.h>
+#include <algorithm>
 #include <atomic>
 #include <ATen/cuda/CUDAContext.h>
 #include <c10/cuda/CUDAGuard.h>
@@ -70,7 +71,7 @@ void gated_head_rms_norm(const Tensor& o, const Tensor& w, c10::optional<Tensor>
 }
 
 void causal_conv_silu(const Tensor& x, const Tensor& w, const Tensor& cu, const Tensor& rows, const Tensor& tok_seq, Tensor window,
-                      Tensor y) {
+                      Tensor y, int64_t max_len) {
   const bool bf16 = act_is_bf16(x, "x");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "x must be [T, C] with unit inner stride");
   const int T = static_cast<int>(x.size(0)), C = static_cast<int>(x.size(1)), taps = static_cast<int>(w.size(1));
@@ -82,7 +83,8 @@ void causal_conv_silu(const Tensor& x, const Tensor& w, const Tensor& cu, const 
   TORCH_CHECK(tok_seq.numel() == T && cu.numel() == rows.numel() + 1, "bad packed-batch tensors");
   c10::cuda::CUDAGuard g(x.device());
   b200seq::causal_conv_silu(x.data_ptr(), x.stride(0), w.data_ptr(), cu.data_ptr<int>(), rows.data_ptr<int>(), tok_seq.data_ptr<int>(),
-                            window.data_ptr(), y.data_ptr(), T, static_cast<int>(rows.numel()), C, taps, bf16, cur_stream());
+                            window.data_ptr(), y.data_ptr(), T, static_cast<int>(rows.numel()), C, taps, static_cast<int>(max_len), bf16,
+                            cur_stream());
   count(2); check_last_error("causal_conv_silu");
 }
 
@@ -107,7 +109,7 @@ void delta_rule_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Te
   p.unit_eps = static_cast<float>(unit_eps); p.q_scale = static_cast<float>(q_scale);
   c10::cuda::CUDAGuard g(q.device());
   TORCH_CHECK(b200seq::delta_rule_scan(p, static_cast<int>(rows.numel()), bf16, cur_stream()), "delta_rule_scan: key dim ", p.d,
-              " above the largest kernel instance (128)");
+              " above the largest kernel instance (256)");
   count(); check_last_error("delta_rule_scan");
 }
 
@@ -135,12 +137,12 @@ void mlstm_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor&
   p.q_scale = static_cast<float>(q_scale); p.denom_eps = static_cast<float>(denom_eps);
   c10::cuda::CUDAGuard g(q.device());
   TORCH_CHECK(b200seq::mlstm_scan(p, static_cast<int>(rows.numel()), bf16, cur_stream()), "mlstm_scan: key dim ", p.d,
-              " above the largest kernel instance (128)");
+              " above the largest kernel instance (256)");
   count(); check_last_error("mlstm_scan");
 }
 
 void latent_attention_paged(const Tensor& q, const Tensor& cache, const Tensor& block_table, const Tensor& tok_req, const Tensor& tok_len,
-                            Tensor out, int64_t block_size, double scale) {
+                            Tensor out, int64_t block_size, double scale, int64_t max_len) {
   const bool bf16 = act_is_bf16(q, "q_lat");
   TORCH_CHECK(q.dim() == 3 && q.is_contiguous(), "q_lat must be contiguous [T, H, r]");
   TORCH_CHECK(cache.scalar_type() == q.scalar_type() && cache.dim() == 2 && cache.is_contiguous() && cache.size(1) == q.size(2),
@@ -155,9 +157,17 @@ void latent_attention_paged(const Tensor& q, const Tensor& cache, const Tensor& 
   p.H = static_cast<int>(q.size(1)); p.r = static_cast<int>(q.size(2)); p.block_size = static_cast<int>(block_size);
   p.max_blocks = static_cast<int>(block_table.size(1)); p.scale = static_cast<float>(scale);
   c10::cuda::CUDAGuard g(q.device());
+  p.n_splits = b200seq::latent_attention_splits(p.H, p.r, static_cast<int>(q.size(0)), static_cast<int>(max_len));
+  const int64_t vec = 16 / static_cast<int64_t>(cache.element_size());
+  p.vec_ok = (p.r % vec == 0 && reinterpret_cast<uintptr_t>(cache.data_ptr()) % 16 == 0) ? 1 : 0;
+  Tensor ws;
+  if (p.n_splits > 1) {
+    ws = torch::empty({q.size(0), q.size(1), p.n_splits, q.size(2) + 2}, out.options());
+    p.ws = ws.data_ptr<float>();
+  }
   TORCH_CHECK(b200seq::latent_attention_paged(p, static_cast<int>(q.size(0)), bf16, cur_stream()), "latent_attention_paged: rank ", p.r,
               " above the largest kernel instance (1024)");
-  count(); check_last_error("latent_attention_paged");
+  count(p.n_splits > 1 ? 2 : 1); check_last_error("latent_attention_paged");
 }
 
 void group_limited_router(const Tensor& logits, Tensor probs, Tensor rmap, int64_t topk, int64_t groups, int64_t keep, bool renorm) {

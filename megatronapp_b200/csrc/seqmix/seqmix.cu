@@ -3,11 +3,12 @@
 //
 // Conventions: activations are `T` (float or __nv_bfloat16); statistics, gates, decays, scores and every recurrent state are
 // fp32.  `cu[R + 1]` holds the sequence boundaries of the packed batch, `rows[R]` the state row of every sequence.
-// The scans keep one column of the d x dv memory per thread in registers (columns never interact), stage q / k / gates of a
-// chunk of tokens in shared memory, and therefore synchronise a few times per chunk instead of per token.
+// The scans keep the d x dv memory in registers, a column per group of four lanes (columns never interact), stage q / k /
+// gates of a chunk of tokens in shared memory, and therefore synchronise a few times per chunk instead of per token.
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <algorithm>
 
 #include "seqmix_api.h"
 
@@ -102,6 +103,52 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, co
   st(y + static_cast<int64_t>(t) * C + c, acc * sigmoidf_(acc));
 }
 
+// Two adjacent channels and a run of kConvRun tokens of one sequence per thread: every input is read once and slides through
+// registers.  grid (channel-pair blocks, runs of the longest sequence, sequences).
+constexpr int kConvRun = 8;
+
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+};
+template <> struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 v) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y);
+  }
+};
+
+template <typename T, int TAPS>
+__global__ void __launch_bounds__(128) causal_conv_silu_run_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w,
+                                                                   const int* __restrict__ cu, const int* __restrict__ rows,
+                                                                   const T* __restrict__ window, T* __restrict__ y, int C) {
+  const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x), r = blockIdx.z;
+  const int a = cu[r], b = cu[r + 1];
+  const int t_lo = a + blockIdx.y * kConvRun, t_hi = min(b, t_lo + kConvRun);
+  if (c >= C || t_lo >= t_hi) return;
+  const T* win = window + static_cast<int64_t>(rows[r]) * (TAPS - 1) * C;
+  float2 wt[TAPS], hist[TAPS];
+#pragma unroll
+  for (int j = 0; j < TAPS; ++j) wt[j] = make_float2(ld(w + static_cast<int64_t>(c) * TAPS + j), ld(w + static_cast<int64_t>(c + 1) * TAPS + j));
+#pragma unroll
+  for (int j = 0; j < TAPS - 1; ++j) {               // hist[j] = input at t_lo - (TAPS - 1) + j
+    const int src = t_lo - (TAPS - 1) + j;
+    hist[j] = src >= a ? Pair<T>::load(x + src * ldx + c) : Pair<T>::load(win + static_cast<int64_t>(TAPS - 1 + (src - a)) * C + c);
+  }
+  for (int t = t_lo; t < t_hi; ++t) {
+    hist[TAPS - 1] = Pair<T>::load(x + t * ldx + c);
+    float2 acc = make_float2(0.f, 0.f);
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) { acc.x = fmaf(wt[j].x, hist[j].x, acc.x); acc.y = fmaf(wt[j].y, hist[j].y, acc.y); }
+    Pair<T>::store(y + static_cast<int64_t>(t) * C + c, make_float2(acc.x * sigmoidf_(acc.x), acc.y * sigmoidf_(acc.y)));
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) hist[j] = hist[j + 1];
+  }
+}
+
 template <typename T>
 __global__ void conv_window_update_kernel(const T* __restrict__ x, int64_t ldx, const int* __restrict__ cu,
                                           const int* __restrict__ rows, T* __restrict__ window, int R, int C, int taps) {
@@ -117,32 +164,47 @@ __global__ void conv_window_update_kernel(const T* __restrict__ x, int64_t ldx, 
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// gated delta rule.  grid (column blocks, heads, sequences); thread j owns column j of S.
+// gated delta rule.  grid (column blocks, heads, sequences).  A column of S is shared by kParts adjacent lanes: lane
+// `part` keeps rows part, part + kParts, ... in registers, so the two reductions over the key dimension per token end in
+// two shuffles and the dependent chains are a quarter as long.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kChunk = 16;     // tokens staged per shared-memory round
-constexpr int kCols = 64;      // columns (threads) per CTA
+constexpr int kParts = 4;
+constexpr int kScanThreads = 128;
+constexpr int kColsPerCta = kScanThreads / kParts;
+template <int D> struct ScanChunk { static constexpr int value = D > 128 ? 8 : 16; };   // tokens staged per shared-memory round
+
+__device__ __forceinline__ float part_sum(float v) {
+  v += __shfl_xor_sync(0xffffffffu, v, 1);
+  v += __shfl_xor_sync(0xffffffffu, v, 2);
+  return v;
+}
 
 template <typename T, int D>
-__global__ void __launch_bounds__(kCols) delta_rule_scan_kernel(DeltaArgs p) {
-  __shared__ float sq[kChunk][D], sk[kChunk][D], sg[kChunk][D];
-  __shared__ float sbeta[kChunk];
+__global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs p) {
+  constexpr int CH = ScanChunk<D>::value, RP = D / kParts;
+  __shared__ float sq[CH][D], sk[CH][D], sg[CH][D];
+  __shared__ float sbeta[CH];
   const int h = blockIdx.y, r = blockIdx.z, kh = h / (p.H / p.KH);
-  const int col = blockIdx.x * kCols + threadIdx.x;
+  const int part = threadIdx.x & (kParts - 1);
+  const int col = blockIdx.x * kColsPerCta + (threadIdx.x >> 2);
   const bool live = col < p.dv;
   const int a = p.cu[r], b = p.cu[r + 1];
   if (a >= b) return;
   float* state = p.state + (static_cast<int64_t>(p.rows[r]) * p.H + h) * p.d * p.dv;
-  float S[D];
+  float S[RP];
 #pragma unroll
-  for (int i = 0; i < D; ++i) S[i] = (live && i < p.d) ? state[static_cast<int64_t>(i) * p.dv + col] : 0.f;
+  for (int e = 0; e < RP; ++e) {
+    const int i = e * kParts + part;
+    S[e] = (live && i < p.d) ? state[static_cast<int64_t>(i) * p.dv + col] : 0.f;
+  }
   const T* q = static_cast<const T*>(p.q);
   const T* k = static_cast<const T*>(p.k);
   const T* v = static_cast<const T*>(p.v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kCols >> 5;
-  for (int t0 = a; t0 < b; t0 += kChunk) {
-    const int nt = min(kChunk, b - t0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kScanThreads >> 5;
+  for (int t0 = a; t0 < b; t0 += CH) {
+    const int nt = min(CH, b - t0);
     __syncthreads();
-    for (int e = threadIdx.x; e < nt * D; e += kCols) {
+    for (int e = threadIdx.x; e < nt * D; e += kScanThreads) {
       const int tt = e / D, i = e % D, t = t0 + tt;
       const bool in = i < p.d;
       sq[tt][i] = in ? ld(q + t * p.ldq + kh * p.d + i) : 0.f;
@@ -160,26 +222,37 @@ __global__ void __launch_bounds__(kCols) delta_rule_scan_kernel(DeltaArgs p) {
       for (int i = lane; i < D; i += 32) { sq[tt][i] *= rq; sk[tt][i] *= rk; }
     }
     __syncthreads();
-    if (live) {
 #pragma unroll 1
-      for (int tt = 0; tt < nt; ++tt) {
-        const int t = t0 + tt;
-        const float vv = ld(v + t * p.ldv + h * p.dv + col);
-        float acc = 0.f;
+    for (int tt = 0; tt < nt; ++tt) {
+      const int t = t0 + tt;
+      const float vv = live ? ld(v + t * p.ldv + h * p.dv + col) : 0.f;
+      float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < D; ++i) { S[i] *= sg[tt][i]; acc = fmaf(S[i], sk[tt][i], acc); }
-        const float u = sbeta[tt] * (vv - acc);
-        float o = 0.f;
-#pragma unroll
-        for (int i = 0; i < D; ++i) { S[i] = fmaf(sk[tt][i], u, S[i]); o = fmaf(S[i], sq[tt][i], o); }
-        p.out[(static_cast<int64_t>(t) * p.H + h) * p.dv + col] = o;
+      for (int e = 0; e < RP; e += 2) {
+        S[e] *= sg[tt][e * kParts + part];
+        acc0 = fmaf(S[e], sk[tt][e * kParts + part], acc0);
+        S[e + 1] *= sg[tt][(e + 1) * kParts + part];
+        acc1 = fmaf(S[e + 1], sk[tt][(e + 1) * kParts + part], acc1);
       }
+      const float u = sbeta[tt] * (vv - part_sum(acc0 + acc1));
+      float o0 = 0.f, o1 = 0.f;
+#pragma unroll
+      for (int e = 0; e < RP; e += 2) {
+        S[e] = fmaf(sk[tt][e * kParts + part], u, S[e]);
+        o0 = fmaf(S[e], sq[tt][e * kParts + part], o0);
+        S[e + 1] = fmaf(sk[tt][(e + 1) * kParts + part], u, S[e + 1]);
+        o1 = fmaf(S[e + 1], sq[tt][(e + 1) * kParts + part], o1);
+      }
+      const float o = part_sum(o0 + o1);
+      if (live && part == 0) p.out[(static_cast<int64_t>(t) * p.H + h) * p.dv + col] = o;
     }
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < D; ++i)
-      if (i < p.d) state[static_cast<int64_t>(i) * p.dv + col] = S[i];
+    for (int e = 0; e < RP; ++e) {
+      const int i = e * kParts + part;
+      if (i < p.d) state[static_cast<int64_t>(i) * p.dv + col] = S[e];
+    }
   }
 }
 
@@ -188,35 +261,40 @@ __global__ void __launch_bounds__(kCols) delta_rule_scan_kernel(DeltaArgs p) {
 // head (they do not depend on the columns) and written back by the first one.
 // ---------------------------------------------------------------------------------------------------------------------
 template <typename T, int D>
-__global__ void __launch_bounds__(kCols) mlstm_scan_kernel(MlstmArgs p) {
-  __shared__ float sq[kChunk][D], sk[kChunk][D], sp[kChunk][D];
-  __shared__ float skeep[kChunk], sput[kChunk], sfloor[kChunk], sden[kChunk];
-  constexpr int NPT = (D + kCols - 1) / kCols;     // normaliser entries per thread
+__global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(MlstmArgs p) {
+  constexpr int CH = ScanChunk<D>::value, RP = D / kParts;
+  __shared__ float sq[CH][D], sk[CH][D], sp[CH][D];
+  __shared__ float skeep[CH], sput[CH], sfloor[CH], sden[CH];
+  constexpr int NPT = (D + kScanThreads - 1) / kScanThreads;     // normaliser entries per thread
   const int h = blockIdx.y, r = blockIdx.z;
-  const int col = blockIdx.x * kCols + threadIdx.x;
+  const int part = threadIdx.x & (kParts - 1);
+  const int col = blockIdx.x * kColsPerCta + (threadIdx.x >> 2);
   const bool live = col < p.dv;
   const int a = p.cu[r], b = p.cu[r + 1];
   if (a >= b) return;
   const int64_t row = p.rows[r];
   float* state = p.state + (row * p.H + h) * p.d * p.dv;
   float* nstate = p.norm_state + (row * p.H + h) * p.d;
-  float S[D], nvec[NPT];
+  float S[RP], nvec[NPT];
 #pragma unroll
-  for (int i = 0; i < D; ++i) S[i] = (live && i < p.d) ? state[static_cast<int64_t>(i) * p.dv + col] : 0.f;
+  for (int e = 0; e < RP; ++e) {
+    const int i = e * kParts + part;
+    S[e] = (live && i < p.d) ? state[static_cast<int64_t>(i) * p.dv + col] : 0.f;
+  }
 #pragma unroll
   for (int e = 0; e < NPT; ++e) {
-    const int i = threadIdx.x + e * kCols;
+    const int i = threadIdx.x + e * kScanThreads;
     nvec[e] = (i < p.d) ? nstate[i] : 0.f;
   }
   float m = p.max_state[row * p.H + h];
   const T* q = static_cast<const T*>(p.q);
   const T* k = static_cast<const T*>(p.k);
   const T* v = static_cast<const T*>(p.v);
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kCols >> 5;
-  for (int t0 = a; t0 < b; t0 += kChunk) {
-    const int nt = min(kChunk, b - t0);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kScanThreads >> 5;
+  for (int t0 = a; t0 < b; t0 += CH) {
+    const int nt = min(CH, b - t0);
     __syncthreads();
-    for (int e = threadIdx.x; e < nt * D; e += kCols) {
+    for (int e = threadIdx.x; e < nt * D; e += kScanThreads) {
       const int tt = e / D, i = e % D, t = t0 + tt;
       const bool in = i < p.d;
       sq[tt][i] = in ? ld(q + t * p.ldq + h * p.d + i) * p.q_scale : 0.f;
@@ -240,7 +318,7 @@ __global__ void __launch_bounds__(kCols) mlstm_scan_kernel(MlstmArgs p) {
     for (int tt = 0; tt < nt; ++tt) {
 #pragma unroll
       for (int e = 0; e < NPT; ++e) {
-        const int i = threadIdx.x + e * kCols;
+        const int i = threadIdx.x + e * kScanThreads;
         if (i < D) {
           nvec[e] = skeep[tt] * nvec[e] + sput[tt] * sk[tt][i];
           sp[tt][i] = nvec[e] * sq[tt][i];
@@ -255,27 +333,34 @@ __global__ void __launch_bounds__(kCols) mlstm_scan_kernel(MlstmArgs p) {
       if (lane == 0) sden[tt] = fmaxf(fabsf(s), sfloor[tt]) + p.denom_eps;
     }
     __syncthreads();
-    if (live) {
 #pragma unroll 1
-      for (int tt = 0; tt < nt; ++tt) {
-        const int t = t0 + tt;
-        const float pv = sput[tt] * ld(v + t * p.ldv + h * p.dv + col), keep = skeep[tt];
-        float o = 0.f;
+    for (int tt = 0; tt < nt; ++tt) {
+      const int t = t0 + tt;
+      const float pv = live ? sput[tt] * ld(v + t * p.ldv + h * p.dv + col) : 0.f;
+      const float keep = skeep[tt];
+      float o0 = 0.f, o1 = 0.f;
 #pragma unroll
-        for (int i = 0; i < D; ++i) { S[i] = fmaf(keep, S[i], sk[tt][i] * pv); o = fmaf(S[i], sq[tt][i], o); }
-        p.out[(static_cast<int64_t>(t) * p.H + h) * p.dv + col] = o / sden[tt];
+      for (int e = 0; e < RP; e += 2) {
+        S[e] = fmaf(keep, S[e], sk[tt][e * kParts + part] * pv);
+        o0 = fmaf(S[e], sq[tt][e * kParts + part], o0);
+        S[e + 1] = fmaf(keep, S[e + 1], sk[tt][(e + 1) * kParts + part] * pv);
+        o1 = fmaf(S[e + 1], sq[tt][(e + 1) * kParts + part], o1);
       }
+      const float o = part_sum(o0 + o1);
+      if (live && part == 0) p.out[(static_cast<int64_t>(t) * p.H + h) * p.dv + col] = o / sden[tt];
     }
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < D; ++i)
-      if (i < p.d) state[static_cast<int64_t>(i) * p.dv + col] = S[i];
+    for (int e = 0; e < RP; ++e) {
+      const int i = e * kParts + part;
+      if (i < p.d) state[static_cast<int64_t>(i) * p.dv + col] = S[e];
+    }
   }
   if (blockIdx.x == 0) {
 #pragma unroll
     for (int e = 0; e < NPT; ++e) {
-      const int i = threadIdx.x + e * kCols;
+      const int i = threadIdx.x + e * kScanThreads;
       if (i < p.d) nstate[i] = nvec[e];
     }
     if (threadIdx.x == 0) p.max_state[row * p.H + h] = m;
@@ -283,79 +368,150 @@ __global__ void __launch_bounds__(kCols) mlstm_scan_kernel(MlstmArgs p) {
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// latent attention over paged latents.  grid (tokens, head groups); each warp walks a strided subset of the visible keys
-// with an online softmax per head, the warps' partial results are merged through shared memory.
+// latent attention over paged latents.  grid (tokens, head blocks, key splits).  The CTA stages tiles of kKeyTile latents
+// in shared memory once for all of its heads; every warp owns HGW heads (queries and accumulators in registers, the latent
+// dimension spread over the lanes) and walks all keys of the CTA's range with an online softmax, kKeyBatch keys at a time so
+// that the score reductions overlap.  With more than one split (few query tokens, long contexts) every warp leaves (max, sum,
+// weighted sum) in a workspace and a second kernel merges the splits.
 // ---------------------------------------------------------------------------------------------------------------------
-constexpr int kAttnWarps = 4;
+constexpr int kAttnWarps = 8;
+constexpr int kKeyTile = 16;
+constexpr int kKeyBatch = 4;
 
-template <typename T, int RPL, int HG>
+template <typename T, int RPL, int HGW>
 __global__ void __launch_bounds__(kAttnWarps * 32) latent_attention_kernel(LatentAttnArgs p) {
-  extern __shared__ float smem[];                   // q [HG][r] | per warp: m [HG], l [HG], acc [HG][r]
-  const int t = blockIdx.x, h0 = blockIdx.y * HG, nh = min(HG, p.H - h0);
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  T* tile = reinterpret_cast<T*>(smem_raw);          // [kKeyTile][r]
+  const int t = blockIdx.x;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int h0 = (blockIdx.y * kAttnWarps + warp) * HGW;
+  const int nh = max(0, min(HGW, p.H - h0));
   const int r = p.r, len = p.tok_len[t];
+  const int per_split = (len + p.n_splits - 1) / p.n_splits;
+  const int key_lo = blockIdx.z * per_split, key_hi = min(len, key_lo + per_split);
   const int* table = p.block_table + static_cast<int64_t>(p.tok_req[t]) * p.max_blocks;
-  float* sq = smem;
-  float* part = smem + HG * r;
-  const T* q = static_cast<const T*>(p.q) + (static_cast<int64_t>(t) * p.H + h0) * r;
-  for (int e = threadIdx.x; e < HG * r; e += blockDim.x) sq[e] = (e / r) < nh ? ld(q + e) * p.scale : 0.f;
-  __syncthreads();
-  float mx[HG], l[HG], acc[HG][RPL];
-#pragma unroll
-  for (int g = 0; g < HG; ++g) {
-    mx[g] = -INFINITY; l[g] = 0.f;
-#pragma unroll
-    for (int e = 0; e < RPL; ++e) acc[g][e] = 0.f;
-  }
   const T* cache = static_cast<const T*>(p.cache);
-  for (int j = warp; j < len; j += kAttnWarps) {
-    const int64_t slot = static_cast<int64_t>(table[j / p.block_size]) * p.block_size + j % p.block_size;
-    float c[RPL];
+  float qv[HGW][RPL], acc[HGW][RPL], mx[HGW], l[HGW];
+#pragma unroll
+  for (int g = 0; g < HGW; ++g) {
+    mx[g] = -INFINITY; l[g] = 0.f;
 #pragma unroll
     for (int e = 0; e < RPL; ++e) {
       const int i = lane + 32 * e;
-      c[e] = i < r ? ld(cache + slot * r + i) : 0.f;
+      qv[g][e] = (g < nh && i < r) ? ld(static_cast<const T*>(p.q) + (static_cast<int64_t>(t) * p.H + h0 + g) * r + i) * p.scale : 0.f;
+      acc[g][e] = 0.f;
     }
+  }
+  constexpr int VEC = 16 / sizeof(T);
+  for (int tile_lo = key_lo; tile_lo < key_hi; tile_lo += kKeyTile) {
+    const int nk = min(kKeyTile, key_hi - tile_lo);
+    __syncthreads();                                  // the previous tile has been consumed
+    for (int j = warp; j < nk; j += kAttnWarps) {
+      const int key = tile_lo + j;
+      const T* src = cache + (static_cast<int64_t>(table[key / p.block_size]) * p.block_size + key % p.block_size) * r;
+      if (p.vec_ok) {
+        for (int i = lane * VEC; i < r; i += 32 * VEC)
+          *reinterpret_cast<uint4*>(tile + j * r + i) = *reinterpret_cast<const uint4*>(src + i);
+      } else {
+        for (int i = lane; i < r; i += 32) tile[j * r + i] = src[i];
+      }
+    }
+    __syncthreads();
+    if (nh == 0) continue;
+    for (int j0 = 0; j0 < nk; j0 += kKeyBatch) {
+      float sc[HGW][kKeyBatch];
 #pragma unroll
-    for (int g = 0; g < HG; ++g) {
-      float s = 0.f;
+      for (int g = 0; g < HGW; ++g)
+#pragma unroll
+        for (int kb = 0; kb < kKeyBatch; ++kb) sc[g][kb] = 0.f;
+#pragma unroll
+      for (int kb = 0; kb < kKeyBatch; ++kb) {
+        if (j0 + kb < nk) {
+#pragma unroll
+          for (int e = 0; e < RPL; ++e) {
+            const int i = lane + 32 * e;
+            const float c = i < r ? ld(tile + (j0 + kb) * r + i) : 0.f;
+#pragma unroll
+            for (int g = 0; g < HGW; ++g) sc[g][kb] = fmaf(qv[g][e], c, sc[g][kb]);
+          }
+        }
+      }
+#pragma unroll
+      for (int g = 0; g < HGW; ++g)
+#pragma unroll
+        for (int kb = 0; kb < kKeyBatch; ++kb) sc[g][kb] = (j0 + kb < nk) ? warp_sum(sc[g][kb]) : -INFINITY;
+      float corr[HGW];
+#pragma unroll
+      for (int g = 0; g < HGW; ++g) {
+        float m_new = mx[g];
+#pragma unroll
+        for (int kb = 0; kb < kKeyBatch; ++kb) m_new = fmaxf(m_new, sc[g][kb]);
+        corr[g] = expf(mx[g] - m_new);
+        float wsum = 0.f;
+#pragma unroll
+        for (int kb = 0; kb < kKeyBatch; ++kb) { sc[g][kb] = expf(sc[g][kb] - m_new); wsum += sc[g][kb]; }
+        l[g] = l[g] * corr[g] + wsum;
+        mx[g] = m_new;
+      }
 #pragma unroll
       for (int e = 0; e < RPL; ++e) {
         const int i = lane + 32 * e;
-        if (i < r) s = fmaf(sq[g * r + i], c[e], s);
+        float c[kKeyBatch];
+#pragma unroll
+        for (int kb = 0; kb < kKeyBatch; ++kb) c[kb] = (i < r && j0 + kb < nk) ? ld(tile + (j0 + kb) * r + i) : 0.f;
+#pragma unroll
+        for (int g = 0; g < HGW; ++g) {
+          float a = acc[g][e] * corr[g];
+#pragma unroll
+          for (int kb = 0; kb < kKeyBatch; ++kb) a = fmaf(sc[g][kb], c[kb], a);
+          acc[g][e] = a;
+        }
       }
-      s = warp_sum(s);
-      const float m_new = fmaxf(mx[g], s);
-      const float corr = expf(mx[g] - m_new), w = expf(s - m_new);
-      l[g] = l[g] * corr + w;
-#pragma unroll
-      for (int e = 0; e < RPL; ++e) acc[g][e] = acc[g][e] * corr + w * c[e];
-      mx[g] = m_new;
     }
   }
-  float* mine = part + static_cast<int64_t>(warp) * HG * (r + 2);
 #pragma unroll
-  for (int g = 0; g < HG; ++g) {
-    if (lane == 0) { mine[g * (r + 2)] = mx[g]; mine[g * (r + 2) + 1] = l[g]; }
+  for (int g = 0; g < HGW; ++g) {
+    if (g >= nh) continue;
+    const int64_t row = static_cast<int64_t>(t) * p.H + h0 + g;
+    if (p.n_splits == 1) {
+      const float inv = 1.0f / l[g];
 #pragma unroll
-    for (int e = 0; e < RPL; ++e) {
-      const int i = lane + 32 * e;
-      if (i < r) mine[g * (r + 2) + 2 + i] = acc[g][e];
+      for (int e = 0; e < RPL; ++e) {
+        const int i = lane + 32 * e;
+        if (i < r) p.out[row * r + i] = acc[g][e] * inv;
+      }
+    } else {
+      float* ws = p.ws + (row * p.n_splits + blockIdx.z) * (r + 2);
+      if (lane == 0) { ws[0] = mx[g]; ws[1] = l[g]; }
+#pragma unroll
+      for (int e = 0; e < RPL; ++e) {
+        const int i = lane + 32 * e;
+        if (i < r) ws[2 + i] = acc[g][e];
+      }
     }
   }
-  __syncthreads();
-  for (int e = threadIdx.x; e < nh * r; e += blockDim.x) {
-    const int g = e / r, i = e % r;
-    float m_all = -INFINITY;
-    for (int w = 0; w < kAttnWarps; ++w) m_all = fmaxf(m_all, part[(w * HG + g) * (r + 2)]);
-    float num = 0.f, den = 0.f;
-    for (int w = 0; w < kAttnWarps; ++w) {
-      const float* pw = part + (w * HG + g) * (r + 2);
-      const float f = pw[0] == -INFINITY ? 0.f : expf(pw[0] - m_all);
-      num += f * pw[2 + i];
-      den += f * pw[1];
+}
+
+// one warp per (token, head): merge the splits' (max, sum, weighted sum)
+__global__ void latent_attention_merge_kernel(const float* __restrict__ ws, float* __restrict__ out, int n_rows, int r, int n_splits) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= n_rows) return;
+  const int lane = threadIdx.x & 31;
+  const float* base = ws + static_cast<int64_t>(row) * n_splits * (r + 2);
+  float m_all = -INFINITY;
+  for (int z = 0; z < n_splits; ++z) m_all = fmaxf(m_all, base[z * (r + 2)]);
+  float den = 0.f;
+  for (int z = 0; z < n_splits; ++z) {
+    const float mz = base[z * (r + 2)];
+    den += (mz == -INFINITY ? 0.f : expf(mz - m_all)) * base[z * (r + 2) + 1];
+  }
+  for (int i = lane; i < r; i += 32) {
+    float num = 0.f;
+    for (int z = 0; z < n_splits; ++z) {
+      const float mz = base[z * (r + 2)];
+      num += (mz == -INFINITY ? 0.f : expf(mz - m_all)) * base[z * (r + 2) + 2 + i];
     }
-    p.out[(static_cast<int64_t>(t) * p.H + h0 + g) * r + i] = num / den;
+    out[static_cast<int64_t>(row) * r + i] = num / den;
   }
 }
 
@@ -454,12 +610,28 @@ void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* 
                            w_per_head ? 1 : 0, eps));
 }
 
+template <typename T, int TAPS>
+static void launch_conv_run(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const void* window, void* y,
+                            int R, int C, int max_len, cudaStream_t s) {
+  dim3 grid((C / 2 + 127) / 128, (max_len + kConvRun - 1) / kConvRun, R);
+  causal_conv_silu_run_kernel<T, TAPS><<<grid, 128, 0, s>>>(static_cast<const T*>(x), ldx, static_cast<const T*>(w), cu, rows,
+                                                            static_cast<const T*>(window), static_cast<T*>(y), C);
+}
+
 void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const int* tok_seq, void* window,
-                      void* y, int n_tok, int R, int C, int taps, bool bf16, cudaStream_t s) {
+                      void* y, int n_tok, int R, int C, int taps, int max_len, bool bf16, cudaStream_t s) {
   if (n_tok == 0) return;
   const int64_t n = static_cast<int64_t>(n_tok) * C;
+  // the paired kernel needs even channel counts and strides, 4- / 8-byte aligned bases, and a grid within the launch limits
+  const size_t pair_bytes = bf16 ? 4 : 8;
+  const bool paired = taps >= 2 && taps <= 4 && C % 2 == 0 && ldx % 2 == 0 && reinterpret_cast<uintptr_t>(x) % pair_bytes == 0 &&
+                      reinterpret_cast<uintptr_t>(y) % pair_bytes == 0 && reinterpret_cast<uintptr_t>(window) % pair_bytes == 0 &&
+                      max_len > 0 && (max_len + kConvRun - 1) / kConvRun <= 65535 && R <= 65535;
   SEQ_DISPATCH_T(bf16, {
-    causal_conv_silu_kernel<T><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
+    if (paired && taps == 2) launch_conv_run<T, 2>(x, ldx, w, cu, rows, window, y, R, C, max_len, s);
+    else if (paired && taps == 3) launch_conv_run<T, 3>(x, ldx, w, cu, rows, window, y, R, C, max_len, s);
+    else if (paired && taps == 4) launch_conv_run<T, 4>(x, ldx, w, cu, rows, window, y, R, C, max_len, s);
+    else causal_conv_silu_kernel<T><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
         static_cast<const T*>(x), ldx, static_cast<const T*>(w), cu, rows, tok_seq, static_cast<const T*>(window),
         static_cast<T*>(y), n_tok, C, taps);
     if (taps > 1)
@@ -470,54 +642,91 @@ void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, 
 
 template <typename T>
 static bool launch_delta(const DeltaArgs& p, dim3 grid, cudaStream_t s) {
-  if (p.d <= 32) delta_rule_scan_kernel<T, 32><<<grid, kCols, 0, s>>>(p);
-  else if (p.d <= 64) delta_rule_scan_kernel<T, 64><<<grid, kCols, 0, s>>>(p);
-  else if (p.d <= 128) delta_rule_scan_kernel<T, 128><<<grid, kCols, 0, s>>>(p);
+  if (p.d <= 32) delta_rule_scan_kernel<T, 32><<<grid, kScanThreads, 0, s>>>(p);
+  else if (p.d <= 64) delta_rule_scan_kernel<T, 64><<<grid, kScanThreads, 0, s>>>(p);
+  else if (p.d <= 128) delta_rule_scan_kernel<T, 128><<<grid, kScanThreads, 0, s>>>(p);
+  else if (p.d <= 256) delta_rule_scan_kernel<T, 256><<<grid, kScanThreads, 0, s>>>(p);
   else return false;
   return true;
 }
 
 bool delta_rule_scan(const DeltaArgs& p, int R, bool bf16, cudaStream_t s) {
   if (R == 0) return true;
-  dim3 grid((p.dv + kCols - 1) / kCols, p.H, R);
+  dim3 grid((p.dv + kColsPerCta - 1) / kColsPerCta, p.H, R);
   return bf16 ? launch_delta<__nv_bfloat16>(p, grid, s) : launch_delta<float>(p, grid, s);
 }
 
 template <typename T>
 static bool launch_mlstm(const MlstmArgs& p, dim3 grid, cudaStream_t s) {
-  if (p.d <= 32) mlstm_scan_kernel<T, 32><<<grid, kCols, 0, s>>>(p);
-  else if (p.d <= 64) mlstm_scan_kernel<T, 64><<<grid, kCols, 0, s>>>(p);
-  else if (p.d <= 128) mlstm_scan_kernel<T, 128><<<grid, kCols, 0, s>>>(p);
+  if (p.d <= 32) mlstm_scan_kernel<T, 32><<<grid, kScanThreads, 0, s>>>(p);
+  else if (p.d <= 64) mlstm_scan_kernel<T, 64><<<grid, kScanThreads, 0, s>>>(p);
+  else if (p.d <= 128) mlstm_scan_kernel<T, 128><<<grid, kScanThreads, 0, s>>>(p);
+  else if (p.d <= 256) mlstm_scan_kernel<T, 256><<<grid, kScanThreads, 0, s>>>(p);
   else return false;
   return true;
 }
 
 bool mlstm_scan(const MlstmArgs& p, int R, bool bf16, cudaStream_t s) {
   if (R == 0) return true;
-  dim3 grid((p.dv + kCols - 1) / kCols, p.H, R);
+  dim3 grid((p.dv + kColsPerCta - 1) / kColsPerCta, p.H, R);
   return bf16 ? launch_mlstm<__nv_bfloat16>(p, grid, s) : launch_mlstm<float>(p, grid, s);
 }
 
-template <typename T, int RPL, int HG>
+template <typename T, int RPL, int HGW>
 static bool launch_attn(const LatentAttnArgs& p, int n_tok, cudaStream_t s) {
-  const size_t smem = (static_cast<size_t>(HG) * p.r + static_cast<size_t>(kAttnWarps) * HG * (p.r + 2)) * sizeof(float);
-  auto kern = latent_attention_kernel<T, RPL, HG>;
+  const size_t smem = static_cast<size_t>(kKeyTile) * p.r * sizeof(T);
+  auto kern = latent_attention_kernel<T, RPL, HGW>;
   if (smem > 48 * 1024 && cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) != cudaSuccess)
     return false;
-  dim3 grid(n_tok, (p.H + HG - 1) / HG);
+  dim3 grid(n_tok, (p.H + kAttnWarps * HGW - 1) / (kAttnWarps * HGW), p.n_splits);
   kern<<<grid, kAttnWarps * 32, smem, s>>>(p);
+  if (p.n_splits > 1) {
+    const int rows = n_tok * p.H;
+    latent_attention_merge_kernel<<<(rows + 3) / 4, 128, 0, s>>>(p.ws, p.out, rows, p.r, p.n_splits);
+  }
   return true;
+}
+
+// latent entries per lane (a power of two >= r / 32) and heads per warp: as many as fit 32 accumulators per lane, but no more
+// than it takes to spread the heads over the CTA's warps
+static void attn_shape(int H, int r, int* rpl, int* hgw) {
+  int e = 2;
+  while (e * 32 < r) e *= 2;
+  int g = 1;
+  while (g < 8 && g * 2 * e <= 32 && kAttnWarps * g < H) g *= 2;
+  *rpl = e; *hgw = g;
+}
+
+template <typename T, int RPL>
+static bool dispatch_attn_hgw(const LatentAttnArgs& p, int hgw, int n_tok, cudaStream_t s) {
+  if (hgw == 1) return launch_attn<T, RPL, 1>(p, n_tok, s);
+  if constexpr (RPL <= 16) { if (hgw == 2) return launch_attn<T, RPL, 2>(p, n_tok, s); }
+  if constexpr (RPL <= 8) { if (hgw == 4) return launch_attn<T, RPL, 4>(p, n_tok, s); }
+  if constexpr (RPL <= 4) { if (hgw == 8) return launch_attn<T, RPL, 8>(p, n_tok, s); }
+  return false;
 }
 
 template <typename T>
 static bool dispatch_attn(const LatentAttnArgs& p, int n_tok, cudaStream_t s) {
-  const int rpl = (p.r + 31) / 32;                  // latent entries per lane; heads per CTA shrink as it grows
-  if (rpl <= 2) return p.H >= 8 ? launch_attn<T, 2, 8>(p, n_tok, s) : launch_attn<T, 2, 4>(p, n_tok, s);
-  if (rpl <= 4) return p.H >= 8 ? launch_attn<T, 4, 8>(p, n_tok, s) : launch_attn<T, 4, 4>(p, n_tok, s);
-  if (rpl <= 8) return launch_attn<T, 8, 4>(p, n_tok, s);
-  if (rpl <= 16) return launch_attn<T, 16, 2>(p, n_tok, s);
-  if (rpl <= 32) return launch_attn<T, 32, 1>(p, n_tok, s);
-  return false;
+  int rpl, hgw;
+  attn_shape(p.H, p.r, &rpl, &hgw);
+  switch (rpl) {
+    case 2: return dispatch_attn_hgw<T, 2>(p, hgw, n_tok, s);
+    case 4: return dispatch_attn_hgw<T, 4>(p, hgw, n_tok, s);
+    case 8: return dispatch_attn_hgw<T, 8>(p, hgw, n_tok, s);
+    case 16: return dispatch_attn_hgw<T, 16>(p, hgw, n_tok, s);
+    case 32: return dispatch_attn_hgw<T, 32>(p, hgw, n_tok, s);
+    default: return false;
+  }
+}
+
+int latent_attention_splits(int H, int r, int n_tok, int max_len) {
+  int rpl, hgw;
+  attn_shape(H, r, &rpl, &hgw);
+  const int64_t ctas = static_cast<int64_t>(n_tok) * ((H + kAttnWarps * hgw - 1) / (kAttnWarps * hgw));
+  if (ctas >= 2 * 148 || max_len < 8 * kKeyTile) return 1;
+  const int64_t want = (4 * 148 + ctas - 1) / ctas;
+  return static_cast<int>(std::max<int64_t>(1, std::min<int64_t>(std::min<int64_t>(want, 64), max_len / (4 * kKeyTile))));
 }
 
 bool latent_attention_paged(const LatentAttnArgs& p, int n_tok, bool bf16, cudaStream_t s) {

@@ -34,7 +34,9 @@ struct LatentAttnArgs {
   const void* cache;              // [slots, r]
   const int *block_table, *tok_req, *tok_len;
   float* out;                     // [T, H, r]
-  int H, r, block_size, max_blocks;
+  float* ws;                      // [T, H, n_splits, r + 2] when n_splits > 1
+  int H, r, block_size, max_blocks, n_splits;
+  int vec_ok;                     // rows of the cache may be copied 16 bytes at a time
   float scale;
 };
 
@@ -42,10 +44,12 @@ void add_rms_norm(float* x, const void* delta, const void* w, void* y, int rows,
 void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* y, int n_tok, int H, int dv, bool w_per_head,
                          float eps, bool bf16, cudaStream_t s);
 void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const int* tok_seq, void* window,
-                      void* y, int n_tok, int R, int C, int taps, bool bf16, cudaStream_t s);
+                      void* y, int n_tok, int R, int C, int taps, int max_len, bool bf16, cudaStream_t s);
 bool delta_rule_scan(const DeltaArgs& p, int R, bool bf16, cudaStream_t s);
 bool mlstm_scan(const MlstmArgs& p, int R, bool bf16, cudaStream_t s);
 bool latent_attention_paged(const LatentAttnArgs& p, int n_tok, bool bf16, cudaStream_t s);
+// key splits per query token for a batch of n_tok tokens whose longest context is max_len
+int latent_attention_splits(int H, int r, int n_tok, int max_len);
 bool group_limited_router(const float* logits, float* probs, bool* rmap, int n_tok, int E, int topk, int G, int keep, bool renorm,
                           cudaStream_t s);
 

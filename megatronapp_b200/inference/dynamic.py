@@ -200,7 +200,7 @@ class DynamicInferenceContext:
             raise RuntimeError(f"layer {layer} has written no latents for this step")
         self.kernel_calls += 1
         return seqmix.latent_attention_paged(q_lat, self.latents[layer], self._block_table, self._tok_req, self._tok_len,
-                                             self.block_size, scale)
+                                             self.block_size, scale, self._max_len)
 
     # -- attention over the paged cache --------------------------------------------
     def attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:

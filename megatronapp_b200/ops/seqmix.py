@@ -141,7 +141,7 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, win
         kernel_calls["causal_conv_silu"] += 1
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
         ext().causal_conv_silu(x if x.stride(1) == 1 else x.contiguous(), weight.contiguous(), pb.cu, pb.slots, pb.tok_seq,
-                               window, y)
+                               window, y, pb.max_len)
         return y
     taps = weight.shape[1]
     w = weight.float()
@@ -245,20 +245,21 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_i: torch.T
 # ---------------------------------------------------------------------------
 
 def latent_attention_paged(q_lat: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor,
-                           tok_len: torch.Tensor, block_size: int, scale: float) -> torch.Tensor:
+                           tok_len: torch.Tensor, block_size: int, scale: float, max_len: int = 0) -> torch.Tensor:
     """Attention of every packed query token over the latents of its own sequence, in the latent space.
 
     ``q_lat [T, H, r]``: the query of head ``h`` already carried into the latent space (``W_uk,h^T q_h``), so that
     ``score = q_lat . c * scale``; ``cache [num_slots, r]``: one latent per cached token, pages of ``block_size`` slots;
     ``block_table [R, max_blocks]``; ``tok_req [T]`` the sequence of each query token, ``tok_len [T]`` how many cached
     tokens it sees (its own included).  Returns ``sum_j softmax_j(score) c_j`` as fp32 ``[T, H, r]``; the caller applies
-    the per-head value up-projection.  Scores, softmax and the weighted sum are fp32."""
+    the per-head value up-projection.  Scores, softmax and the weighted sum are fp32.  ``max_len`` (the longest visible
+    context, known to the host) lets the kernel split long contexts over several CTAs when the batch has few tokens."""
     T, H, r = q_lat.shape
     if q_lat.is_cuda:
         kernel_calls["latent_attention_paged"] += 1
         o = torch.empty(T, H, r, dtype=torch.float32, device=q_lat.device)
         ext().latent_attention_paged(q_lat.contiguous(), cache, block_table, tok_req, tok_len, o, int(block_size),
-                                     float(scale))
+                                     float(scale), int(max_len))
         return o
     o = torch.empty(T, H, r, dtype=torch.float32)
     req, lens = tok_req.tolist(), tok_len.tolist()

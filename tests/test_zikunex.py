@@ -342,3 +342,65 @@ def test_config_rejects_a_latent_source_that_owns_nothing():
     bad = config_of([layer(LAT, kv_from=1), layer(LAT, kv_from=0)])
     with pytest.raises(ValueError):
         ZikunexConfig.from_dict(bad)
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# model folder -> registry -> trace runner / generation command line
+# ---------------------------------------------------------------------------------------------------------------------
+def write_model_folder(path, cfg, W):
+    """``config.json`` + ``model.safetensors`` (bf16 tensors; 8-byte header length, JSON header, raw data)."""
+    import json
+    import struct
+
+    with open(path / "config.json", "w") as f:
+        json.dump(cfg, f)
+    header, blobs, off = {}, [], 0
+    for k, v in W.items():
+        b = v.to(torch.bfloat16).contiguous().view(torch.uint8).numpy().tobytes()
+        header[k] = {"dtype": "BF16", "shape": list(v.shape), "data_offsets": [off, off + len(b)]}
+        off += len(b)
+        blobs.append(b)
+    h = json.dumps(header).encode()
+    with open(path / "model.safetensors", "wb") as f:
+        f.write(struct.pack("<Q", len(h)) + h + b"".join(blobs))
+
+
+def test_model_folder_through_registry_trace_runner_and_cli(tmp_path):
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cfg = config_of([layer(DELTA, MOE_A), layer(LAT), layer(MLSTM_B, {"kind": "dense", "ff": 40}), layer(LAT, kv_from=1)])
+    W = {k: v.to(torch.bfloat16).float() for k, v in oracle.random_weights(cfg, 5, low_rank=12).items()}
+    write_model_folder(tmp_path, cfg, W)
+    a, b = tokens_of(19, seed=20), tokens_of(6, seed=21)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": a[:16], "want": [0, 7, 15]}, {"id": "y", "tokens": b[:4], "want": [3]}], "end": []},
+             {"step": 1, "entries": [{"id": "x", "tokens": a[16:17], "want": []}, {"id": "y", "tokens": b[4:5], "want": [0]}], "end": []},
+             {"step": 2, "entries": [{"id": "x", "tokens": a[17:18], "want": [0]}, {"id": "y", "tokens": b[5:6], "want": [0]}], "end": ["y"]},
+             {"step": 3, "entries": [{"id": "x", "tokens": a[18:19], "want": [0]}], "end": ["x"]}]
+    out = tmp_path / "out"
+    env = dict(os.environ, CUDA_VISIBLE_DEVICES="")
+    r = subprocess.run([os.path.join(root, "bin", "trace_run"), "--model", str(tmp_path), "--dtype", "float32", "--out", str(out),
+                        "--max-tokens", "64"], input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                       env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert [l for l in r.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2", "done 3"]
+    wa, wb = oracle.forward(cfg, W, a), oracle.forward(cfg, W, b)
+    got = {n: torch.from_numpy(np.fromfile(out / f"{n}.f32", dtype="<f4").reshape(-1, 96).copy()) for n in (0, 1, 2, 3)}
+    close(got[0], torch.stack([wa[0], wa[7], wa[15], wb[3]]), TOL[torch.float32])
+    close(got[1], wb[4:5], TOL[torch.float32])
+    close(got[2], torch.stack([wa[17], wb[5]]), TOL[torch.float32])
+    close(got[3], wa[18:19], TOL[torch.float32])
+    # the generation command line on the same folder: greedy tokens of the oracle
+    r = subprocess.run([sys.executable, os.path.join(root, "tools", "run_text_generation_server.py"), "--model-dir", str(tmp_path),
+                        "--dtype", "float32", "--prompts", " ".join(map(str, b)), "--num-tokens-to-generate", "4"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    toks = list(b)
+    for _ in range(4):
+        toks.append(int(oracle.forward(cfg, W, toks)[-1].argmax()))
+    assert r.stdout.strip().splitlines()[-1].endswith("-> " + repr(" ".join(map(str, toks[len(b):]))))

@@ -1,6 +1,12 @@
 #!/usr/bin/env python
 """Text generation server (reference ``tools/run_text_generation_server.py``): REST on --port, or
-the MegaScope WebSocket protocol with --enable-ws-server.  Loads ``--load`` if given."""
+the MegaScope WebSocket protocol with --enable-ws-server.  Loads ``--load`` if given.
+
+``--model-dir DIR`` serves a *model folder* (``config.json`` naming a registered architecture + ``model.safetensors``)
+instead of a Megatron checkpoint: the model registry builds it and the dynamic engine serves it, e.g.
+
+    python tools/run_text_generation_server.py --model-dir DIR --dtype bfloat16 --prompts "5 9 23" --num-tokens-to-generate 16
+"""
 import os
 import sys
 
@@ -29,7 +35,46 @@ def add_text_generate_args(parser):
     return parser
 
 
+def main_model_dir(argv=None):
+    """Serve a model folder through the registry and the dynamic engine (token-id prompts with the null tokenizer)."""
+    import argparse
+
+    import torch
+
+    from megatronapp_b200.data.tokenizer import NullTokenizer
+    from megatronapp_b200.inference import DynamicInferenceEngine, SamplingParams
+    from megatronapp_b200.models.registry import build_model_from_dir
+
+    ap = add_text_generate_args(argparse.ArgumentParser(description="serve a model folder"))
+    ap.add_argument("--model-dir", required=True)
+    ap.add_argument("--dtype", choices=("bfloat16", "float32"), default="bfloat16")
+    ap.add_argument("--port", type=int, default=5000)
+    ap.add_argument("--inference-max-seq-length", type=int, default=4096)
+    ap.add_argument("--inference-max-requests", type=int, default=16)
+    ap.add_argument("--cache-tokens", type=int, default=65536, help="tokens the paged cache holds over all requests")
+    ap.add_argument("--block-size", type=int, default=16)
+    ap.add_argument("--seed", type=int, default=None)
+    a = ap.parse_args(argv)
+    dev = "cuda:0" if torch.cuda.is_available() else "cpu"
+    model = build_model_from_dir(a.model_dir, torch.bfloat16 if a.dtype == "bfloat16" else torch.float32, dev)
+    tok = NullTokenizer(model.vocab_size - 1)
+    n_req = a.max_batch_size_override or a.inference_max_requests
+    engine = DynamicInferenceEngine(model, tok, a.inference_max_seq_length, a.cache_tokens // a.block_size + n_req, a.block_size,
+                                    max_tokens_per_step=2048, max_requests=n_req, random_seed=a.seed)
+    if a.prompts:
+        sp = SamplingParams(temperature=a.temperature, top_k=a.top_k, top_p=a.top_p, return_log_probs=a.return_log_probs,
+                            num_tokens_to_generate=a.num_tokens_to_generate)
+        for r in engine.generate(list(a.prompts), sp):
+            print(f"{r.prompt!r} -> {r.generated_text!r}", flush=True)
+        return
+    engine.start_background_loop()
+    MegatronServer(engine).run("0.0.0.0" if os.environ.get("B200_BIND_ALL") else "127.0.0.1", a.port)
+
+
 def main(provider=None, extra_args_provider=None):
+    if any(x == "--model-dir" or x.startswith("--model-dir=") for x in sys.argv[1:]):
+        return main_model_dir()
+
     def extra(parser):
         parser = add_text_generate_args(parser)
         return extra_args_provider(parser) if extra_args_provider else parser
