@@ -183,6 +183,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs p) {
   constexpr int CH = ScanChunk<D>::value, RP = D / kParts;
   __shared__ float sq[CH][D], sk[CH][D], sg[CH][D];
+  __shared__ float sv[CH][kColsPerCta];
   __shared__ float sbeta[CH];
   const int h = blockIdx.y, r = blockIdx.z, kh = h / (p.H / p.KH);
   const int part = threadIdx.x & (kParts - 1);
@@ -211,6 +212,10 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs
       sk[tt][i] = in ? ld(k + t * p.ldk + kh * p.d + i) : 0.f;
       sg[tt][i] = in ? expf(p.log_decay[(static_cast<int64_t>(t) * p.H + h) * p.d + i]) : 1.f;
     }
+    for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {   // this CTA's value columns of the chunk
+      const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
+      sv[tt][e % kColsPerCta] = c < p.dv ? ld(v + (t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
+    }
     if (threadIdx.x < nt) sbeta[threadIdx.x] = p.beta[static_cast<int64_t>(t0 + threadIdx.x) * p.H + h];
     __syncthreads();
     for (int tt = warp; tt < nt; tt += n_warps) {     // unit length (and the query's scale)
@@ -225,7 +230,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs
 #pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const int t = t0 + tt;
-      const float vv = live ? ld(v + t * p.ldv + h * p.dv + col) : 0.f;
+      const float vv = sv[tt][threadIdx.x >> 2];
       float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
       for (int e = 0; e < RP; e += 2) {
@@ -264,6 +269,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(MlstmArgs p) {
   constexpr int CH = ScanChunk<D>::value, RP = D / kParts;
   __shared__ float sq[CH][D], sk[CH][D], sp[CH][D];
+  __shared__ float sv[CH][kColsPerCta];
   __shared__ float skeep[CH], sput[CH], sfloor[CH], sden[CH];
   constexpr int NPT = (D + kScanThreads - 1) / kScanThreads;     // normaliser entries per thread
   const int h = blockIdx.y, r = blockIdx.z;
@@ -299,6 +305,10 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(MlstmArgs p) {
       const bool in = i < p.d;
       sq[tt][i] = in ? ld(q + t * p.ldq + h * p.d + i) * p.q_scale : 0.f;
       sk[tt][i] = in ? ld(k + t * p.ldk + h * p.d + i) : 0.f;
+    }
+    for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {   // this CTA's value columns of the chunk
+      const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
+      sv[tt][e % kColsPerCta] = c < p.dv ? ld(v + (t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
     }
     if (threadIdx.x == 0) {                          // the gate recurrence is scalar: one thread walks the chunk
       float mm = m;
@@ -336,7 +346,7 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(MlstmArgs p) {
 #pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const int t = t0 + tt;
-      const float pv = live ? sput[tt] * ld(v + t * p.ldv + h * p.dv + col) : 0.f;
+      const float pv = sput[tt] * sv[tt][threadIdx.x >> 2];
       const float keep = skeep[tt];
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll

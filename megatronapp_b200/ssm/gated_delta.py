@@ -5,9 +5,9 @@ Per head a matrix memory ``S [d, dv]`` is carried from token to token::
     g = exp(-exp(A_log) * softplus(W_a2 W_a1 h + dt_bias))          (one value per key channel)
     S <- g[:, None] * S;  u = beta * (v - S^T k);  S <- S + k u^T;  o = S^T q
 
-with ``beta = sigmoid(W_b h)``, q / k / v each passed through a short causal depth-wise convolution and SiLU, q and k
-scaled to unit length per head (q also by ``d^-1/2``), and the read-out divided by its root mean square per head, scaled
-by a weight shared by the heads and gated by ``sigmoid(W_g2 W_g1 h)``.  Grouped heads: value head ``h`` uses q / k head
+with ``beta = sigmoid(W_b h)``.  q, k and v come out of a short causal depth-wise convolution + SiLU; q and k are then
+normalised to unit length head by head (q additionally times ``d^-1/2``).  The read-out is RMS-normalised per head with
+one weight vector common to all heads and gated by ``sigmoid(W_g2 W_g1 h)``.  Grouped heads: value head ``h`` uses q / k head
 ``h // (heads / kv_heads)``.
 
 The module keeps the framework's Mamba mixer shape (``ssm/mamba.py``): one fused input projection whose rows are the

@@ -6,8 +6,9 @@ Per head, with log gates ``i = cap * tanh((W_i h + b_i) / cap)`` and ``f = logsi
     S <- e^(f + m - m') S + e^(i - m') k v^T          n <- e^(f + m - m') n + e^(i - m') k
     o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)        (q carries the d^-1/2 factor)
 
-``S``, ``n`` and ``m`` start at zero.  Every head's read-out is divided by its root mean square, the concatenation is
-scaled by a weight over all heads' channels and gated by ``sigmoid(W_g h)``, then projected out.  As in the framework's
+All three parts of the state are zero before a sequence's first token (the maximum too: it is not minus infinity).
+The read-out is RMS-normalised head by head, the concatenated heads are scaled by one weight vector over all their
+channels and gated by ``sigmoid(W_g h)``, then projected out.  As in the framework's
 other recurrent mixers one fused input projection produces the segments ``[q | k | v | g | i | f]``, the state lives in
 the inference context, and gates, maxima and the memory are fp32.
 

@@ -282,7 +282,8 @@ def test_delta_rule_recalls_an_early_write_after_hundreds_of_tokens(device):
 
 @pytest.mark.parametrize("device", DEVICES)
 def test_mlstm_gates_with_large_and_small_maxima(device):
-    """Input gates far above and far below the running maximum, which starts at 0 and not at minus infinity."""
+    """Input gates far above and far below the running maximum; a fresh sequence begins with maximum 0, so tiny early gates
+    must be weighed against e^0 and not against themselves."""
     T, H, d, dv = 70, 2, 12, 66
     g = torch.Generator().manual_seed(2)
     q, k, v = torch.randn(T, H, d, generator=g), torch.randn(T, H, d, generator=g), torch.randn(T, H, dv, generator=g)
