@@ -72,6 +72,7 @@ class DynamicInferenceContext:
         self.states: Dict[object, torch.Tensor] = {}   # key -> recurrent state [max_requests, ...]
         self._free_rows = list(range(max_requests - 1, -1, -1))
         self.packed = None                             # ops.seqmix.PackedBatch of the current step
+        self.fresh_prefill, self.min_new = False, 0
         self._device = None
         self.use_paged_kernel = os.environ.get("B200_PAGED_ATTN", "1") == "1"     # 0: gather + einsum reference path
         self.kernel_calls = 0
@@ -154,6 +155,9 @@ class DynamicInferenceContext:
             mask[i, :n, :L] = torch.arange(L).unsqueeze(0) <= qpos
             mask[i, n:, 0] = True                                      # padded query rows: keep softmax finite
         self._plan = plan
+        # a step in which every sequence begins (nothing cached yet): layers may run dense prefill kernels on it
+        self.fresh_prefill = all(p[3] == 0 for p in plan)
+        self.min_new = min(p[2] for p in plan)
         self.packed = PackedBatch([p[1] for p in plan] + [q0], [self.seqs[p[0]].state_row for p in plan], device)
         # paged-attention kernel inputs: the request row and the number of visible keys of every packed query token, and
         # the block tables of this step's requests
@@ -184,6 +188,19 @@ class DynamicInferenceContext:
         return {rid: qs + n - 1 for rid, qs, n, _ in self._plan}
 
     # -- latent attention over the paged cache ----------------------------------------
+    def write_latents(self, layer: int, c_new: torch.Tensor) -> None:
+        """Store this step's latents ``[T, r]`` of ``layer`` in their pages."""
+        if layer not in self.latents:
+            self.latents[layer] = torch.zeros(self.num_blocks * self.block_size, c_new.shape[-1], dtype=c_new.dtype,
+                                              device=c_new.device)
+        self.latents[layer][self._write_slots] = c_new
+
+    def step_latents(self, layer: int) -> torch.Tensor:
+        """The latents ``[T, r]`` that ``layer`` wrote for this step's tokens (for a layer that shares them)."""
+        if layer not in self.latents:
+            raise RuntimeError(f"layer {layer} has written no latents for this step")
+        return self.latents[layer][self._write_slots]
+
     def attend_latent(self, layer: int, q_lat: torch.Tensor, c_new: Optional[torch.Tensor], scale: float) -> torch.Tensor:
         """``q_lat [T, H, r]`` (queries carried into the latent space) against the latent pages of ``layer``.  ``c_new
         [T, r]`` are this step's latents, written into their pages first; a layer that shares another layer's latents
@@ -192,10 +209,7 @@ class DynamicInferenceContext:
         from ..ops import seqmix
 
         if c_new is not None:
-            if layer not in self.latents:
-                self.latents[layer] = torch.zeros(self.num_blocks * self.block_size, c_new.shape[-1], dtype=c_new.dtype,
-                                                  device=c_new.device)
-            self.latents[layer][self._write_slots] = c_new
+            self.write_latents(layer, c_new)
         elif layer not in self.latents:
             raise RuntimeError(f"layer {layer} has written no latents for this step")
         self.kernel_calls += 1

@@ -23,7 +23,7 @@ from .dynamic import DynamicInferenceEngine
 
 
 class TraceReplayer:
-    def __init__(self, model, max_tokens: int, block_size: int = 16, max_requests: int = 64,
+    def __init__(self, model, max_tokens: int, block_size: int = 16, max_requests: int = 256,
                  max_sequence_length: Optional[int] = None):
         from ..data.tokenizer import NullTokenizer
 

@@ -160,8 +160,14 @@ class LatentSelfAttention(MegatronModule):
     Decoding and chunked prefill never expand the cache into keys and values: the query is carried into the latent
     space (``q_lat = W_uk,h^T q_h``), one paged kernel computes ``softmax(q_lat . c * scale)`` and the weighted sum of
     latents for all heads of a token (each cached row is read once), and ``W_uv,h`` is applied to that sum.
+    A step in which every sequence starts (fresh prompts) has all its keys at hand: with 16-bit activations and a head
+    shape the tcgen05 flash kernel takes (``qk_dim == v_dim`` in 64 / 128, prompts of ``FLASH_PREFILL_MIN_TOKENS`` or more)
+    K and V are expanded from the step's latents and the prompts run through ``ops.attention_varlen``; the latents still
+    go to their pages for the steps that follow (``B200_LATENT_FLASH_PREFILL=0`` keeps the paged kernel for everything).
     Tensor parallel: heads are split (``W_uq / W_uk / W_uv`` column-parallel, ``W_o`` row-parallel), the latents are
     replicated."""
+
+    FLASH_PREFILL_MIN_TOKENS = 64
 
     def __init__(self, config, layer_number: int, num_heads: int, qk_dim: int, v_dim: int, kv_rank: int, q_rank: int,
                  softmax_scale: float, kv_source_layer: Optional[int] = None, eps: Optional[float] = None):
@@ -197,6 +203,13 @@ class LatentSelfAttention(MegatronModule):
                                              init_method=config.output_layer_init_method, bias=False,
                                              input_is_parallel=True, skip_bias_add=True)
 
+    def _flash_prefill(self, q, ctx) -> bool:
+        import os
+
+        return (ctx.fresh_prefill and ctx.min_new >= self.FLASH_PREFILL_MIN_TOKENS and q.is_cuda
+                and q.dtype in (torch.bfloat16, torch.float16) and self.qk_dim == self.v_dim and self.qk_dim in (64, 128)
+                and os.environ.get("B200_LATENT_FLASH_PREFILL", "1") == "1" and ops.native_attention_available())
+
     @property
     def cache_layer(self) -> int:
         """The layer whose latents this layer attends over."""
@@ -212,6 +225,16 @@ class LatentSelfAttention(MegatronModule):
             kvc, _ = self.linear_kv_down_proj(hidden_states)
             c = self.kv_layernorm(kvc)                                      # [s, b, r]
         if inference_context is not None and not inference_context.is_static_batching():
+            if self._flash_prefill(q, inference_context):
+                if c is not None:
+                    inference_context.write_latents(self.layer_number, c[:, 0])
+                c_step = c[:, 0] if c is not None else inference_context.step_latents(self.cache_layer)
+                k, _ = self.linear_k_up_proj(c_step)
+                v, _ = self.linear_v_up_proj(c_step)
+                cu = inference_context.packed.cu_host
+                o = ops.attention_varlen(q[:, 0], k.view(s, self.nh_local, self.qk_dim), v.view(s, self.nh_local, self.v_dim),
+                                         (cu, cu), None, self.softmax_scale, True, 0.0, False)
+                return self.linear_proj(o.reshape(s, 1, self.nh_local * self.v_dim))
             # packed tokens [T, 1, ...] against the paged latent cache
             wk = self.linear_k_up_proj.weight.view(self.nh_local, self.qk_dim, self.kv_rank)
             wv = self.linear_v_up_proj.weight.view(self.nh_local, self.v_dim, self.kv_rank)

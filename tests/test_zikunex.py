@@ -208,6 +208,45 @@ def test_bfloat16_serving_stays_within_rounding():
     assert seqmix.kernel_calls["delta_rule_scan"] and seqmix.kernel_calls["latent_attention_paged"]
 
 
+@pytest.mark.gpu
+def test_fresh_prompts_through_the_flash_kernel_match_the_paged_kernel_and_the_oracle(monkeypatch):
+    """bf16 prompts with a head shape the tcgen05 flash kernel takes are expanded to K / V for their first step; lengths off
+    the kernel's tile sizes, two prompts in one step, a layer that shares latents, then decoding from the pages."""
+    from megatronapp_b200 import ops
+
+    lat64 = {"type": "latent_attention", "mixer": {"heads": 3, "dim": 64, "vdim": 64, "kv_rank": 40, "q_rank": 24, "scale": 0.15}}
+    cfg = config_of([layer(lat64, {"kind": "dense", "ff": 96}), layer(MLSTM_B), layer(lat64, kv_from=0)])
+    model, W = build(cfg, "cuda", torch.bfloat16)
+    Wb = {k: v.to(torch.bfloat16).float() for k, v in W.items()}
+    reqs = {"a": tokens_of(203, seed=30), "b": tokens_of(70, seed=31)}
+    want = {k: oracle.forward(cfg, Wb, v) for k, v in reqs.items()}
+
+    def run(flag):
+        monkeypatch.setenv("B200_LATENT_FLASH_PREFILL", flag)
+        rp = replayer(model, max_tokens=1024, block_size=16)
+        first = {"a": 199, "b": 65}
+        outs = {k: [] for k in reqs}
+        o = rp.step([{"id": k, "tokens": reqs[k][:first[k]], "want": list(range(first[k]))} for k in reqs])
+        outs["a"].append(o[:199])
+        outs["b"].append(o[199:])
+        for j in range(4):
+            o = rp.step([{"id": k, "tokens": [reqs[k][first[k] + j]], "want": [0]} for k in reqs])
+            outs["a"].append(o[0:1])
+            outs["b"].append(o[1:2])
+        return {k: torch.cat(v) for k, v in outs.items()}
+
+    before = ops.fallback_counts["attention_sdpa"]
+    flash, paged_ = run("1"), run("0")
+    assert ops.fallback_counts["attention_sdpa"] == before and ops.native_attention_available()
+    for k in reqs:
+        n = flash[k].shape[0]
+        for got in (flash[k], paged_[k]):
+            d = got.double().cpu() - want[k][:n]
+            d = d - d.mean(-1, keepdim=True)
+            rel = d.pow(2).mean(-1).sqrt() / want[k][:n].std(-1)
+            assert rel.median().item() < 0.03 and rel.max().item() < 0.2, (k, rel.median().item(), rel.max().item())
+
+
 # ---------------------------------------------------------------------------------------------------------------------
 # ops with inputs made so that one far entry decides the result
 # ---------------------------------------------------------------------------------------------------------------------
