@@ -140,20 +140,7 @@ class DynamicInferenceContext:
             plan.append((rid, q0, n_new, s.kv_len))
             q0 += n_new
         R = len(plan)
-        n_max = max(p[2] for p in plan)
         l_max = max(p[2] + p[3] for p in plan)
-        q_index = torch.zeros(R, n_max, dtype=torch.long)
-        q_valid = torch.zeros(R, n_max, dtype=torch.bool)
-        kv_slots = torch.zeros(R, l_max, dtype=torch.long)
-        mask = torch.zeros(R, n_max, l_max, dtype=torch.bool)        # True = may attend
-        for i, (rid, qs, n, before) in enumerate(plan):
-            q_index[i, :n] = torch.arange(qs, qs + n)
-            q_valid[i, :n] = True
-            L = before + n
-            kv_slots[i, :L] = self._slot(self.seqs[rid], torch.arange(L))
-            qpos = torch.arange(before, L).unsqueeze(1)
-            mask[i, :n, :L] = torch.arange(L).unsqueeze(0) <= qpos
-            mask[i, n:, 0] = True                                      # padded query rows: keep softmax finite
         self._plan = plan
         # a step in which every sequence begins (nothing cached yet): layers may run dense prefill kernels on it
         self.fresh_prefill = all(p[3] == 0 for p in plan)
@@ -175,9 +162,32 @@ class DynamicInferenceContext:
         self._max_len = l_max
         self.positions = torch.cat(pos_all).to(device)
         self._write_slots = torch.cat(slots_all).to(device)
+        self._q_index = self._q_valid = self._kv_slots = self._mask = None      # gather path: built on first use
+        return self.positions
+
+    def _ensure_gather(self, device):
+        """Padded gather indices and the visibility mask of the step, for the gather + einsum attention path only (they
+        grow with requests x new tokens x context, which the paged kernels never need)."""
+        if self._mask is not None:
+            return
+        plan = self._plan
+        R = len(plan)
+        n_max = max(p[2] for p in plan)
+        l_max = max(p[2] + p[3] for p in plan)
+        q_index = torch.zeros(R, n_max, dtype=torch.long)
+        q_valid = torch.zeros(R, n_max, dtype=torch.bool)
+        kv_slots = torch.zeros(R, l_max, dtype=torch.long)
+        mask = torch.zeros(R, n_max, l_max, dtype=torch.bool)        # True = may attend
+        for i, (rid, qs, n, before) in enumerate(plan):
+            q_index[i, :n] = torch.arange(qs, qs + n)
+            q_valid[i, :n] = True
+            L = before + n
+            kv_slots[i, :L] = self._slot(self.seqs[rid], torch.arange(L))
+            qpos = torch.arange(before, L).unsqueeze(1)
+            mask[i, :n, :L] = torch.arange(L).unsqueeze(0) <= qpos
+            mask[i, n:, 0] = True                                      # padded query rows: keep softmax finite
         self._q_index, self._q_valid = q_index.to(device), q_valid.to(device)
         self._kv_slots, self._mask = kv_slots.to(device), mask.to(device)
-        return self.positions
 
     def end_step(self):
         for rid, _, n, _ in self._plan:
@@ -238,6 +248,7 @@ class DynamicInferenceContext:
                 self.kernel_calls += 1
                 return ext.paged_attention(q.contiguous(), kc, vc, self._block_table, self._tok_req, self._tok_len,
                                            self.block_size, float(scale), splits)
+        self._ensure_gather(q.device)
         qp = q[self._q_index]                                        # [R, n, np, hn]
         kp, vp = kc[self._kv_slots], vc[self._kv_slots]               # [R, L, ng, hn]
         if np_ != ng:

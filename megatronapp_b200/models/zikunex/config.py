@@ -49,9 +49,8 @@ class ZikunexConfig:
         for i, l in enumerate(layers):
             src = l.mixer.get("kv_from")
             if src is not None:
-                if not (0 <= src < len(layers)) or layers[src].type != "latent_attention" or \
-                        layers[src].mixer.get("kv_from") is not None:
-                    raise ValueError(f"layer {i}: kv_from must name a latent_attention layer that owns its latents")
+                if not (0 <= src < i) or layers[src].type != "latent_attention" or layers[src].mixer.get("kv_from") is not None:
+                    raise ValueError(f"layer {i}: kv_from must name an earlier latent_attention layer that owns its latents")
                 if layers[src].mixer["kv_rank"] != l.mixer["kv_rank"]:
                     raise ValueError(f"layer {i}: kv_rank differs from that of layer {src}")
         return cls(vocab=int(d["vocab"]), width=int(d["width"]), layers=layers,

@@ -53,13 +53,25 @@ def read_safetensors(path: str) -> Dict[str, torch.Tensor]:
 
 
 def shapes_into_config(config: dict, shapes: Dict[str, list]) -> dict:
-    """Fill the sizes ``config.json`` leaves to the tensor shapes (low-rank decay / gate widths) into the mixer dicts."""
+    """Fill the sizes ``config.json`` leaves to the tensor shapes into the mixer dicts: always the low-rank decay / gate
+    widths of ``channel_delta``; the latent ranks and the number of convolution taps only where the file omits them."""
+    def dim(i, name, axis):
+        t = shapes.get(f"l{i}.mix.{name}")
+        return None if t is None else int(t[axis])
+
     for i, l in enumerate(config["layers"]):
+        mx = l["mixer"]
         if l["type"] == "channel_delta":
             for key, name in (("decay_rank", "a1"), ("gate_rank", "g1")):
-                t = shapes.get(f"l{i}.mix.{name}")
-                if t is not None:
-                    l["mixer"][key] = int(t[0])
+                if dim(i, name, 0) is not None:
+                    mx[key] = dim(i, name, 0)
+            if "conv" not in mx and dim(i, "q.conv", 1) is not None:
+                mx["conv"] = dim(i, "q.conv", 1)
+        elif l["type"] == "latent_attention":
+            if "q_rank" not in mx and dim(i, "dq", 0) is not None:
+                mx["q_rank"] = dim(i, "dq", 0)
+            if "kv_rank" not in mx and dim(i, "uk", 1) is not None:
+                mx["kv_rank"] = dim(i, "uk", 1)
     return config
 
 
@@ -70,8 +82,9 @@ def _copy(param: torch.Tensor, src: torch.Tensor, name: str, rows: Tuple[int, in
     dst.copy_(src.to(dst.dtype))
 
 
-def load_zikunex_weights(model, tensors: Dict[str, torch.Tensor], strict: bool = True) -> None:
-    """Copy checkpoint tensors into ``model`` (a ``ZikunexModel`` on a single tensor-parallel rank)."""
+def load_zikunex_weights(model, tensors: Dict[str, torch.Tensor], strict: bool = True):
+    """Copy checkpoint tensors into ``model`` (a ``ZikunexModel`` on a single tensor-parallel rank).  A tensor the model
+    needs must be there; tensors the model has no parameter for raise under ``strict`` and are returned otherwise."""
     used = set()
 
     def take(name):
@@ -126,10 +139,10 @@ def load_zikunex_weights(model, tensors: Dict[str, torch.Tensor], strict: bool =
         if mlp.shared_experts is not None:
             _copy(mlp.shared_experts.linear_fc1.weight, take(m + "shared.up"), m + "shared.up")
             _copy(mlp.shared_experts.linear_fc2.weight, take(m + "shared.down"), m + "shared.down")
-    if strict:
-        extra = sorted(set(tensors) - used)
-        if extra:
-            raise ValueError(f"checkpoint tensors without a parameter: {extra[:8]}{' ...' if len(extra) > 8 else ''}")
+    extra = sorted(set(tensors) - used)
+    if extra and strict:
+        raise ValueError(f"checkpoint tensors without a parameter: {extra[:8]}{' ...' if len(extra) > 8 else ''}")
+    return extra
 
 
 def load_model_dir(path: str, params_dtype=torch.bfloat16, device=None, **config_overrides):
@@ -154,7 +167,11 @@ def load_model_dir(path: str, params_dtype=torch.bfloat16, device=None, **config
                                         **config_overrides)
     model = ZikunexModel(zcfg, base)
     if tensors is not None:
-        load_zikunex_weights(model, tensors)
+        extra = load_zikunex_weights(model, tensors, strict=False)
+        if extra:
+            import sys
+
+            print(f"[zikunex] {len(extra)} checkpoint tensors have no parameter and were ignored: {extra[:4]}", file=sys.stderr)
     if device is not None:
         model = model.to(device)
     return model.eval()
