@@ -89,7 +89,7 @@ void causal_conv_silu(const Tensor& x, const Tensor& w, const Tensor& cu, const 
 }
 
 void delta_rule_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& log_decay, const Tensor& beta, const Tensor& cu,
-                     const Tensor& rows, Tensor state, Tensor out, double unit_eps, double q_scale) {
+                     const Tensor& rows, Tensor state, Tensor out, double unit_eps, double q_scale, int64_t max_len) {
   const bool bf16 = act_is_bf16(q, "q");
   TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(), "q / k / v dtypes differ");
   check_rows(q, "q"); check_rows(k, "k"); check_rows(v, "v");
@@ -107,6 +107,7 @@ void delta_rule_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Te
   p.cu = cu.data_ptr<int>(); p.rows = rows.data_ptr<int>();
   p.state = state.data_ptr<float>(); p.out = out.data_ptr<float>();
   p.unit_eps = static_cast<float>(unit_eps); p.q_scale = static_cast<float>(q_scale);
+  p.max_len = max_len > 0 ? static_cast<int>(max_len) : (1 << 30);
   c10::cuda::CUDAGuard g(q.device());
   TORCH_CHECK(b200seq::delta_rule_scan(p, static_cast<int>(rows.numel()), bf16, cur_stream()), "delta_rule_scan: key dim ", p.d,
               " above the largest kernel instance (256)");
@@ -114,7 +115,8 @@ void delta_rule_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Te
 }
 
 void mlstm_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor& log_i, const Tensor& log_f, const Tensor& cu,
-                const Tensor& rows, Tensor state, Tensor norm_state, Tensor max_state, Tensor out, double q_scale, double denom_eps) {
+                const Tensor& rows, Tensor state, Tensor norm_state, Tensor max_state, Tensor out, double q_scale, double denom_eps,
+                int64_t max_len) {
   const bool bf16 = act_is_bf16(q, "q");
   TORCH_CHECK(k.scalar_type() == q.scalar_type() && v.scalar_type() == q.scalar_type(), "q / k / v dtypes differ");
   check_rows(q, "q"); check_rows(k, "k"); check_rows(v, "v");
@@ -135,6 +137,7 @@ void mlstm_scan(const Tensor& q, const Tensor& k, const Tensor& v, const Tensor&
   p.state = state.data_ptr<float>(); p.norm_state = norm_state.data_ptr<float>(); p.max_state = max_state.data_ptr<float>();
   p.out = out.data_ptr<float>();
   p.q_scale = static_cast<float>(q_scale); p.denom_eps = static_cast<float>(denom_eps);
+  p.max_len = max_len > 0 ? static_cast<int>(max_len) : (1 << 30);
   c10::cuda::CUDAGuard g(q.device());
   TORCH_CHECK(b200seq::mlstm_scan(p, static_cast<int>(rows.numel()), bf16, cur_stream()), "mlstm_scan: key dim ", p.d,
               " above the largest kernel instance (256)");

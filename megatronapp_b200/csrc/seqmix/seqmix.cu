@@ -179,7 +179,7 @@ __device__ __forceinline__ float part_sum(float v) {
   return v;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool PF>
 __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs p) {
   constexpr int CH = ScanChunk<D>::value, RP = D / kParts;
   __shared__ float sq[CH][D], sk[CH][D], sg[CH][D];
@@ -202,21 +202,57 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs
   const T* k = static_cast<const T*>(p.k);
   const T* v = static_cast<const T*>(p.v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kScanThreads >> 5;
+  // With PF (sequences longer than a chunk) the next chunk's inputs are fetched into registers before the sequential part of
+  // the current one, so that their latency hides behind it; they move to shared memory (decays exponentiated) once the current
+  // chunk is done.  Without PF (decoding) a chunk is fetched when its turn comes, which keeps the registers free for occupancy.
+  constexpr int NS = CH * D / kScanThreads, NV = (CH * kColsPerCta + kScanThreads - 1) / kScanThreads;
+  float pq[NS], pk[NS], pg[NS], pv[NV], pbeta = 0.f;
+  auto prefetch = [&](int t0, int nt) {
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const int e = threadIdx.x + s * kScanThreads, tt = e / D, i = e % D, t = t0 + tt;
+      const bool in = tt < nt && i < p.d;
+      pq[s] = in ? ld(q + t * p.ldq + kh * p.d + i) : 0.f;
+      pk[s] = in ? ld(k + t * p.ldk + kh * p.d + i) : 0.f;
+      pg[s] = in ? p.log_decay[(static_cast<int64_t>(t) * p.H + h) * p.d + i] : 0.f;
+    }
+#pragma unroll
+    for (int s = 0; s < NV; ++s) {
+      const int e = threadIdx.x + s * kScanThreads, tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
+      pv[s] = (tt < nt && c < p.dv) ? ld(v + (t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
+    }
+    if (threadIdx.x < nt) pbeta = p.beta[static_cast<int64_t>(t0 + threadIdx.x) * p.H + h];
+  };
+  if (PF) prefetch(a, min(CH, b - a));
   for (int t0 = a; t0 < b; t0 += CH) {
     const int nt = min(CH, b - t0);
-    __syncthreads();
-    for (int e = threadIdx.x; e < nt * D; e += kScanThreads) {
-      const int tt = e / D, i = e % D, t = t0 + tt;
-      const bool in = i < p.d;
-      sq[tt][i] = in ? ld(q + t * p.ldq + kh * p.d + i) : 0.f;
-      sk[tt][i] = in ? ld(k + t * p.ldk + kh * p.d + i) : 0.f;
-      sg[tt][i] = in ? expf(p.log_decay[(static_cast<int64_t>(t) * p.H + h) * p.d + i]) : 1.f;
+    __syncthreads();                                  // the previous chunk has been consumed
+    if constexpr (PF) {
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const int e = threadIdx.x + s * kScanThreads, tt = e / D, i = e % D;
+        if (tt < nt) { sq[tt][i] = pq[s]; sk[tt][i] = pk[s]; sg[tt][i] = expf(pg[s]); }
+      }
+#pragma unroll
+      for (int s = 0; s < NV; ++s) {
+        const int e = threadIdx.x + s * kScanThreads;
+        if (e < nt * kColsPerCta) sv[e / kColsPerCta][e % kColsPerCta] = pv[s];
+      }
+      if (threadIdx.x < nt) sbeta[threadIdx.x] = pbeta;
+    } else {
+      for (int e = threadIdx.x; e < nt * D; e += kScanThreads) {
+        const int tt = e / D, i = e % D, t = t0 + tt;
+        const bool in = i < p.d;
+        sq[tt][i] = in ? ld(q + t * p.ldq + kh * p.d + i) : 0.f;
+        sk[tt][i] = in ? ld(k + t * p.ldk + kh * p.d + i) : 0.f;
+        sg[tt][i] = in ? expf(p.log_decay[(static_cast<int64_t>(t) * p.H + h) * p.d + i]) : 1.f;
+      }
+      for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {
+        const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
+        sv[tt][e % kColsPerCta] = c < p.dv ? ld(v + (t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
+      }
+      if (threadIdx.x < nt) sbeta[threadIdx.x] = p.beta[static_cast<int64_t>(t0 + threadIdx.x) * p.H + h];
     }
-    for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {   // this CTA's value columns of the chunk
-      const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
-      sv[tt][e % kColsPerCta] = c < p.dv ? ld(v + (t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
-    }
-    if (threadIdx.x < nt) sbeta[threadIdx.x] = p.beta[static_cast<int64_t>(t0 + threadIdx.x) * p.H + h];
     __syncthreads();
     for (int tt = warp; tt < nt; tt += n_warps) {     // unit length (and the query's scale)
       float qq = 0.f, kk = 0.f;
@@ -227,6 +263,7 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs
       for (int i = lane; i < D; i += 32) { sq[tt][i] *= rq; sk[tt][i] *= rk; }
     }
     __syncthreads();
+    if (PF && t0 + CH < b) prefetch(t0 + CH, min(CH, b - t0 - CH));
 #pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const int t = t0 + tt;
@@ -265,12 +302,12 @@ __global__ void __launch_bounds__(kScanThreads) delta_rule_scan_kernel(DeltaArgs
 // mLSTM.  Same layout; the normaliser n (a d-vector) and the running maximum m are advanced by every column block of a
 // head (they do not depend on the columns) and written back by the first one.
 // ---------------------------------------------------------------------------------------------------------------------
-template <typename T, int D>
+template <typename T, int D, bool PF>
 __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(MlstmArgs p) {
   constexpr int CH = ScanChunk<D>::value, RP = D / kParts;
   __shared__ float sq[CH][D], sk[CH][D], sp[CH][D];
   __shared__ float sv[CH][kColsPerCta];
-  __shared__ float skeep[CH], sput[CH], sfloor[CH], sden[CH];
+  __shared__ float skeep[CH], sput[CH], sfloor[CH], sden[CH], sli[CH], slf[CH];
   constexpr int NPT = (D + kScanThreads - 1) / kScanThreads;     // normaliser entries per thread
   const int h = blockIdx.y, r = blockIdx.z;
   const int part = threadIdx.x & (kParts - 1);
@@ -297,23 +334,63 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(MlstmArgs p) {
   const T* k = static_cast<const T*>(p.k);
   const T* v = static_cast<const T*>(p.v);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kScanThreads >> 5;
+  constexpr int NS = CH * D / kScanThreads, NV = (CH * kColsPerCta + kScanThreads - 1) / kScanThreads;
+  float pq[NS], pk[NS], pv[NV], pli = 0.f, plf = 0.f;
+  auto prefetch = [&](int t0, int nt) {              // the next chunk's inputs, in flight during the sequential part
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const int e = threadIdx.x + s * kScanThreads, tt = e / D, i = e % D, t = t0 + tt;
+      const bool in = tt < nt && i < p.d;
+      pq[s] = in ? ld(q + t * p.ldq + h * p.d + i) * p.q_scale : 0.f;
+      pk[s] = in ? ld(k + t * p.ldk + h * p.d + i) : 0.f;
+    }
+#pragma unroll
+    for (int s = 0; s < NV; ++s) {
+      const int e = threadIdx.x + s * kScanThreads, tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
+      pv[s] = (tt < nt && c < p.dv) ? ld(v + (t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
+    }
+    if (threadIdx.x < nt) {
+      pli = p.log_i[static_cast<int64_t>(t0 + threadIdx.x) * p.H + h];
+      plf = p.log_f[static_cast<int64_t>(t0 + threadIdx.x) * p.H + h];
+    }
+  };
+  if (PF) prefetch(a, min(CH, b - a));
   for (int t0 = a; t0 < b; t0 += CH) {
     const int nt = min(CH, b - t0);
+    __syncthreads();                                  // the previous chunk has been consumed
+    if constexpr (PF) {
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const int e = threadIdx.x + s * kScanThreads, tt = e / D, i = e % D;
+        if (tt < nt) { sq[tt][i] = pq[s]; sk[tt][i] = pk[s]; }
+      }
+#pragma unroll
+      for (int s = 0; s < NV; ++s) {
+        const int e = threadIdx.x + s * kScanThreads;
+        if (e < nt * kColsPerCta) sv[e / kColsPerCta][e % kColsPerCta] = pv[s];
+      }
+      if (threadIdx.x < nt) { sli[threadIdx.x] = pli; slf[threadIdx.x] = plf; }
+    } else {
+      for (int e = threadIdx.x; e < nt * D; e += kScanThreads) {
+        const int tt = e / D, i = e % D, t = t0 + tt;
+        const bool in = i < p.d;
+        sq[tt][i] = in ? ld(q + t * p.ldq + h * p.d + i) * p.q_scale : 0.f;
+        sk[tt][i] = in ? ld(k + t * p.ldk + h * p.d + i) : 0.f;
+      }
+      for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {
+        const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
+        sv[tt][e % kColsPerCta] = c < p.dv ? ld(v + (t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
+      }
+      if (threadIdx.x < nt) {
+        sli[threadIdx.x] = p.log_i[static_cast<int64_t>(t0 + threadIdx.x) * p.H + h];
+        slf[threadIdx.x] = p.log_f[static_cast<int64_t>(t0 + threadIdx.x) * p.H + h];
+      }
+    }
     __syncthreads();
-    for (int e = threadIdx.x; e < nt * D; e += kScanThreads) {
-      const int tt = e / D, i = e % D, t = t0 + tt;
-      const bool in = i < p.d;
-      sq[tt][i] = in ? ld(q + t * p.ldq + h * p.d + i) * p.q_scale : 0.f;
-      sk[tt][i] = in ? ld(k + t * p.ldk + h * p.d + i) : 0.f;
-    }
-    for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {   // this CTA's value columns of the chunk
-      const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
-      sv[tt][e % kColsPerCta] = c < p.dv ? ld(v + (t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
-    }
     if (threadIdx.x == 0) {                          // the gate recurrence is scalar: one thread walks the chunk
       float mm = m;
       for (int tt = 0; tt < nt; ++tt) {
-        const float li = p.log_i[static_cast<int64_t>(t0 + tt) * p.H + h], lf = p.log_f[static_cast<int64_t>(t0 + tt) * p.H + h];
+        const float li = sli[tt], lf = slf[tt];
         const float m_new = fmaxf(lf + mm, li);
         skeep[tt] = expf(lf + mm - m_new);
         sput[tt] = expf(li - m_new);
@@ -343,6 +420,7 @@ __global__ void __launch_bounds__(kScanThreads) mlstm_scan_kernel(MlstmArgs p) {
       if (lane == 0) sden[tt] = fmaxf(fabsf(s), sfloor[tt]) + p.denom_eps;
     }
     __syncthreads();
+    if (PF && t0 + CH < b) prefetch(t0 + CH, min(CH, b - t0 - CH));
 #pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const int t = t0 + tt;
@@ -652,11 +730,15 @@ void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, 
 
 template <typename T>
 static bool launch_delta(const DeltaArgs& p, dim3 grid, cudaStream_t s) {
-  if (p.d <= 32) delta_rule_scan_kernel<T, 32><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 64) delta_rule_scan_kernel<T, 64><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 128) delta_rule_scan_kernel<T, 128><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 256) delta_rule_scan_kernel<T, 256><<<grid, kScanThreads, 0, s>>>(p);
+#define SEQ_DELTA(DD)                                                                                   \
+  if (p.max_len > ScanChunk<DD>::value) delta_rule_scan_kernel<T, DD, true><<<grid, kScanThreads, 0, s>>>(p); \
+  else delta_rule_scan_kernel<T, DD, false><<<grid, kScanThreads, 0, s>>>(p)
+  if (p.d <= 32) { SEQ_DELTA(32); }
+  else if (p.d <= 64) { SEQ_DELTA(64); }
+  else if (p.d <= 128) { SEQ_DELTA(128); }
+  else if (p.d <= 256) { SEQ_DELTA(256); }
   else return false;
+#undef SEQ_DELTA
   return true;
 }
 
@@ -668,11 +750,15 @@ bool delta_rule_scan(const DeltaArgs& p, int R, bool bf16, cudaStream_t s) {
 
 template <typename T>
 static bool launch_mlstm(const MlstmArgs& p, dim3 grid, cudaStream_t s) {
-  if (p.d <= 32) mlstm_scan_kernel<T, 32><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 64) mlstm_scan_kernel<T, 64><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 128) mlstm_scan_kernel<T, 128><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 256) mlstm_scan_kernel<T, 256><<<grid, kScanThreads, 0, s>>>(p);
+#define SEQ_MLSTM(DD)                                                                              \
+  if (p.max_len > ScanChunk<DD>::value) mlstm_scan_kernel<T, DD, true><<<grid, kScanThreads, 0, s>>>(p); \
+  else mlstm_scan_kernel<T, DD, false><<<grid, kScanThreads, 0, s>>>(p)
+  if (p.d <= 32) { SEQ_MLSTM(32); }
+  else if (p.d <= 64) { SEQ_MLSTM(64); }
+  else if (p.d <= 128) { SEQ_MLSTM(128); }
+  else if (p.d <= 256) { SEQ_MLSTM(256); }
   else return false;
+#undef SEQ_MLSTM
   return true;
 }
 

@@ -15,6 +15,7 @@ struct DeltaArgs {
   float* state;                   // [rows, H, d, dv]
   float* out;                     // [T, H, dv]
   int H, KH, d, dv;
+  int max_len;                    // the longest sequence of the step (0: unknown)
   float unit_eps, q_scale;        // unit_eps < 0: q / k are used as given
 };
 
@@ -26,6 +27,7 @@ struct MlstmArgs {
   float *state, *norm_state, *max_state;
   float* out;
   int H, d, dv;
+  int max_len;                    // the longest sequence of the step (0: unknown)
   float q_scale, denom_eps;
 };
 

@@ -178,7 +178,8 @@ def delta_rule_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_decay
         kernel_calls["delta_rule_scan"] += 1
         o = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
         ext().delta_rule_scan(_rows3(q), _rows3(k), _rows3(v), log_decay.contiguous(), beta.contiguous(),
-                              pb.cu, pb.slots, state, o, -1.0 if unit_eps is None else float(unit_eps), float(q_scale))
+                              pb.cu, pb.slots, state, o, -1.0 if unit_eps is None else float(unit_eps), float(q_scale),
+                              pb.max_len)
         return o
     qf, kf, vf = q.float(), k.float(), v.float()
     if unit_eps is not None:
@@ -220,7 +221,7 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, log_i: torch.T
         kernel_calls["mlstm_scan"] += 1
         o = torch.empty(T, H, dv, dtype=torch.float32, device=q.device)
         ext().mlstm_scan(_rows3(q), _rows3(k), _rows3(v), log_i.contiguous(), log_f.contiguous(),
-                         pb.cu, pb.slots, state, norm_state, max_state, o, float(q_scale), float(denom_eps))
+                         pb.cu, pb.slots, state, norm_state, max_state, o, float(q_scale), float(denom_eps), pb.max_len)
         return o
     qf, kf, vf = q.float() * q_scale, k.float(), v.float()
     li, lf = log_i.float(), log_f.float()

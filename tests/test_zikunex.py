@@ -190,6 +190,24 @@ def test_greedy_generation_through_the_engine(device):
     assert eng.context.allocator.free == 24 and not eng.context.seqs
 
 
+def test_preempted_request_recomputes_its_state_from_zero():
+    """Out of pages in mid-decode: the engine evicts a request (pages and state row go back) and prefills it again later;
+    a state row that kept anything of the first attempt would change the tokens."""
+    cfg = config_of([layer(DELTA, {"kind": "dense", "ff": 48}), layer(LAT), layer(MLSTM_B, MOE_A)])
+    model, W = build(cfg, "cpu")
+    eng = DynamicInferenceEngine(model, NullTokenizer(95), max_sequence_length=64, num_blocks=8, block_size=4,
+                                 max_tokens_per_step=16, max_requests=3)
+    prompts = [tokens_of(4, seed=40), tokens_of(4, seed=41), tokens_of(4, seed=42)]
+    out = eng.generate([" ".join(map(str, p)) for p in prompts], SamplingParams(top_k=1, num_tokens_to_generate=10))
+    assert eng.num_preemptions >= 1
+    for p, o in zip(prompts, out):
+        toks = list(p)
+        for _ in range(o.generated_length):
+            toks.append(int(oracle.forward(cfg, W, toks)[-1, :96].argmax()))
+        assert toks[len(p):] == o.generated_tokens.tolist()
+    assert eng.context.allocator.free == 8 and len(eng.context._free_rows) == 3
+
+
 @pytest.mark.gpu
 def test_bfloat16_serving_stays_within_rounding():
     """bf16 projections around fp32 state, scores and residual.  A router's close call may flip an expert under bf16
