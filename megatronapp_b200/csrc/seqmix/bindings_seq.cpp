@@ -34,7 +34,7 @@ void check_last_error(const char* what) {
   TORCH_CHECK(e == cudaSuccess, what, ": ", cudaGetErrorString(e));
 }
 
-void add_rms_norm(Tensor x, c10::optional<Tensor> delta, const Tensor& w, Tensor y, double eps) {
+void add_rms_norm(Tensor x, c10::optional<Tensor> delta, const Tensor& w, Tensor y, double eps, double w_off) {
   check_f32(x, "x");
   const bool bf16 = act_is_bf16(y, "y");
   TORCH_CHECK(x.dim() == 2 && y.is_contiguous() && y.sizes() == x.sizes(), "x / y must be [rows, cols]");
@@ -48,7 +48,7 @@ void add_rms_norm(Tensor x, c10::optional<Tensor> delta, const Tensor& w, Tensor
   }
   c10::cuda::CUDAGuard g(x.device());
   b200seq::add_rms_norm(x.data_ptr<float>(), d, w.data_ptr(), y.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
-                        static_cast<float>(eps), bf16, cur_stream());
+                        static_cast<float>(eps), static_cast<float>(w_off), bf16, cur_stream());
   count(); check_last_error("add_rms_norm");
 }
 
@@ -70,8 +70,8 @@ void gated_head_rms_norm(const Tensor& o, const Tensor& w, c10::optional<Tensor>
   count(); check_last_error("gated_head_rms_norm");
 }
 
-void causal_conv_silu(const Tensor& x, const Tensor& w, const Tensor& cu, const Tensor& rows, const Tensor& tok_seq, Tensor window,
-                      Tensor y, int64_t max_len) {
+void causal_conv(const Tensor& x, const Tensor& w, const Tensor& cu, const Tensor& rows, const Tensor& tok_seq, Tensor window,
+                 Tensor y, int64_t max_len, bool silu) {
   const bool bf16 = act_is_bf16(x, "x");
   TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1, "x must be [T, C] with unit inner stride");
   const int T = static_cast<int>(x.size(0)), C = static_cast<int>(x.size(1)), taps = static_cast<int>(w.size(1));
@@ -83,7 +83,7 @@ void causal_conv_silu(const Tensor& x, const Tensor& w, const Tensor& cu, const 
   TORCH_CHECK(tok_seq.numel() == T && cu.numel() == rows.numel() + 1, "bad packed-batch tensors");
   c10::cuda::CUDAGuard g(x.device());
   b200seq::causal_conv_silu(x.data_ptr(), x.stride(0), w.data_ptr(), cu.data_ptr<int>(), rows.data_ptr<int>(), tok_seq.data_ptr<int>(),
-                            window.data_ptr(), y.data_ptr(), T, static_cast<int>(rows.numel()), C, taps, static_cast<int>(max_len), bf16,
+                            window.data_ptr(), y.data_ptr(), T, static_cast<int>(rows.numel()), C, taps, static_cast<int>(max_len), silu, bf16,
                             cur_stream());
   count(2); check_last_error("causal_conv_silu");
 }
@@ -185,16 +185,181 @@ void group_limited_router(const Tensor& logits, Tensor probs, Tensor rmap, int64
   count(); check_last_error("group_limited_router");
 }
 
+
+// ---- side-by-side mixer, minGRU, clamped gated activation ------------------------------------------------------------------
+const void* opt_ptr(const c10::optional<Tensor>& t) { return (t.has_value() && t->defined()) ? t->data_ptr() : nullptr; }
+void check_act2(const Tensor& t, const Tensor& like, const char* name) {   // [T, C], unit inner stride, free row stride
+  TORCH_CHECK(t.is_cuda() && t.dim() == 2 && t.stride(1) == 1 && t.scalar_type() == like.scalar_type(), name,
+              " must be a [T, C] CUDA tensor with unit inner stride in the activation dtype");
+}
+
+void norm_add(Tensor x, const Tensor& a, c10::optional<Tensor> b, c10::optional<Tensor> wa, c10::optional<Tensor> wb, const Tensor& w,
+              Tensor y, double eps, double w_off) {
+  check_f32(x, "x");
+  const bool bf16 = act_is_bf16(y, "y");
+  TORCH_CHECK(x.dim() == 2 && y.is_contiguous() && y.sizes() == x.sizes(), "x / y must be [rows, cols]");
+  TORCH_CHECK(a.scalar_type() == y.scalar_type() && a.is_contiguous() && a.sizes() == x.sizes(), "a must be contiguous, shaped like x");
+  TORCH_CHECK(w.scalar_type() == y.scalar_type() && w.is_contiguous() && w.numel() == x.size(1), "bad weight");
+  TORCH_CHECK(x.size(1) * sizeof(float) <= 48 * 1024, "row too wide");
+  const bool two = b.has_value() && b->defined();
+  if (two) {
+    TORCH_CHECK(b->scalar_type() == y.scalar_type() && b->is_contiguous() && b->sizes() == x.sizes(), "b must be shaped like a");
+    TORCH_CHECK(wa.has_value() && wb.has_value() && wa->scalar_type() == y.scalar_type() && wb->scalar_type() == y.scalar_type() &&
+                wa->is_contiguous() && wb->is_contiguous() && wa->numel() == x.size(1) && wb->numel() == x.size(1), "bad branch weights");
+  }
+  c10::cuda::CUDAGuard g(x.device());
+  b200seq::norm_add(x.data_ptr<float>(), a.data_ptr(), two ? b->data_ptr() : nullptr, two ? wa->data_ptr() : nullptr,
+                    two ? wb->data_ptr() : nullptr, w.data_ptr(), y.data_ptr(), static_cast<int>(x.size(0)), static_cast<int>(x.size(1)),
+                    static_cast<float>(eps), static_cast<float>(w_off), bf16, cur_stream());
+  count(); check_last_error("norm_add");
+}
+
+void norm_rope(const Tensor& q, const Tensor& k, const Tensor& wq, const Tensor& wk, const Tensor& positions, const Tensor& inv_freq,
+               Tensor q_out, Tensor k_out, int64_t head_dim, int64_t rot, double eps) {
+  const bool bf16 = act_is_bf16(q, "q");
+  check_act2(q, q, "q"); check_act2(k, q, "k");
+  check_f32(inv_freq, "inv_freq");
+  TORCH_CHECK(positions.is_cuda() && positions.scalar_type() == at::kLong && positions.is_contiguous() && positions.numel() == q.size(0),
+              "positions must be a contiguous int64 [T]");
+  TORCH_CHECK(rot % 2 == 0 && rot <= head_dim && inv_freq.numel() * 2 == rot, "rot must be even, at most head_dim, with rot / 2 frequencies");
+  TORCH_CHECK(q.size(1) % head_dim == 0 && k.size(1) % head_dim == 0 && k.size(0) == q.size(0), "bad q / k shape");
+  TORCH_CHECK(wq.scalar_type() == q.scalar_type() && wk.scalar_type() == q.scalar_type() && wq.is_contiguous() && wk.is_contiguous() &&
+              wq.numel() == q.size(1) && wk.numel() == k.size(1), "bad norm weights");
+  TORCH_CHECK(q_out.scalar_type() == q.scalar_type() && k_out.scalar_type() == q.scalar_type() && q_out.is_contiguous() &&
+              k_out.is_contiguous() && q_out.numel() == q.numel() && k_out.numel() == k.numel(), "bad outputs");
+  TORCH_CHECK(std::max(q.size(1), k.size(1)) * sizeof(float) <= 48 * 1024, "projection too wide");
+  b200seq::NormRopeArgs p{};
+  p.q = q.data_ptr(); p.k = k.data_ptr(); p.ldq = q.stride(0); p.ldk = k.stride(0);
+  p.wq = wq.data_ptr(); p.wk = wk.data_ptr(); p.positions = positions.data_ptr<int64_t>(); p.inv_freq = inv_freq.data_ptr<float>();
+  p.q_out = q_out.data_ptr(); p.k_out = k_out.data_ptr();
+  p.q_ch = static_cast<int>(q.size(1)); p.k_ch = static_cast<int>(k.size(1)); p.head_dim = static_cast<int>(head_dim);
+  p.rot = static_cast<int>(rot); p.eps = static_cast<float>(eps);
+  c10::cuda::CUDAGuard g(q.device());
+  b200seq::norm_rope(p, static_cast<int>(q.size(0)), bf16, cur_stream());
+  count(); check_last_error("norm_rope");
+}
+
+void mixed_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor& vcache, const Tensor& block_table, const Tensor& tok_req,
+                           const Tensor& tok_len, c10::optional<Tensor> talk, c10::optional<Tensor> gate, Tensor out, int64_t block_size,
+                           double scale, int64_t max_len) {
+  const bool bf16 = act_is_bf16(q, "q");
+  check_rows(q, "q");
+  TORCH_CHECK(kcache.scalar_type() == q.scalar_type() && vcache.scalar_type() == q.scalar_type() && kcache.dim() == 3 && vcache.dim() == 3 &&
+              kcache.is_contiguous() && vcache.is_contiguous() && kcache.size(2) == q.size(2) && vcache.size(1) == kcache.size(1),
+              "caches must be contiguous [slots, G, d] / [slots, G, dv] in q's dtype");
+  check_i32(block_table, "block_table"); check_i32(tok_req, "tok_req"); check_i32(tok_len, "tok_len");
+  b200seq::MixAttnArgs p{};
+  p.H = static_cast<int>(q.size(1)); p.G = static_cast<int>(kcache.size(1)); p.d = static_cast<int>(q.size(2));
+  p.dv = static_cast<int>(vcache.size(2));
+  TORCH_CHECK(block_table.dim() == 2 && tok_req.numel() == q.size(0) && tok_len.numel() == q.size(0), "bad packed-batch tensors");
+  TORCH_CHECK(out.scalar_type() == q.scalar_type() && out.is_contiguous() && out.numel() == q.size(0) * p.H * p.dv, "bad out");
+  p.q = q.data_ptr(); p.ldq = q.stride(0); p.kcache = kcache.data_ptr(); p.vcache = vcache.data_ptr();
+  p.block_table = block_table.data_ptr<int>(); p.tok_req = tok_req.data_ptr<int>(); p.tok_len = tok_len.data_ptr<int>();
+  if (talk.has_value() && talk->defined()) {
+    check_f32(*talk, "talk");
+    TORCH_CHECK(talk->numel() == static_cast<int64_t>(p.H) * p.H, "talk must be [H, H]");
+    p.talk = talk->data_ptr<float>();
+  }
+  if (gate.has_value() && gate->defined()) {
+    check_act2(*gate, q, "gate");
+    TORCH_CHECK(gate->size(0) == q.size(0) && gate->size(1) == p.H * p.dv, "gate must be [T, H * dv]");
+    p.gate = gate->data_ptr(); p.ldg = gate->stride(0);
+  }
+  p.out = out.data_ptr();
+  p.block_size = static_cast<int>(block_size); p.max_blocks = static_cast<int>(block_table.size(1)); p.scale = static_cast<float>(scale);
+  c10::cuda::CUDAGuard g(q.device());
+  p.n_splits = b200seq::mixed_attention_splits(static_cast<int>(q.size(0)), static_cast<int>(max_len));
+  Tensor ws1, ws2;
+  if (p.n_splits > 1) {
+    auto o32 = q.options().dtype(at::kFloat);
+    ws1 = torch::empty({q.size(0), p.n_splits, p.H, 2}, o32);
+    ws2 = torch::empty({q.size(0), p.n_splits, static_cast<int64_t>(p.H) * p.dv}, o32);
+    p.ws_stats = ws1.data_ptr<float>(); p.ws_acc = ws2.data_ptr<float>();
+  }
+  TORCH_CHECK(b200seq::mixed_attention_paged(p, static_cast<int>(q.size(0)), bf16, cur_stream()),
+              "mixed_attention_paged: no kernel instance for heads ", p.H, " / ", p.G, ", dims ", p.d, " / ", p.dv);
+  count(p.n_splits > 1 ? 3 : 1); check_last_error("mixed_attention_paged");
+}
+
+void gen_delta_scan(const Tensor& r, const Tensor& k, const Tensor& v, const Tensor& w_pre, const Tensor& a_pre, c10::optional<Tensor> w_bias,
+                    const Tensor& cu, const Tensor& rows, Tensor state, Tensor out, double decay_scale, double unit_eps) {
+  const bool bf16 = act_is_bf16(r, "r");
+  check_rows(r, "r"); check_rows(k, "k"); check_rows(v, "v");
+  check_act2(w_pre, r, "w_pre"); check_act2(a_pre, r, "a_pre");
+  TORCH_CHECK(k.scalar_type() == r.scalar_type() && v.scalar_type() == r.scalar_type(), "r / k / v dtypes differ");
+  check_f32(state, "state"); check_f32(out, "out"); check_i32(cu, "cu"); check_i32(rows, "rows");
+  b200seq::GenDeltaArgs p{};
+  p.H = static_cast<int>(r.size(1)); p.d = static_cast<int>(r.size(2)); p.dv = static_cast<int>(v.size(2));
+  TORCH_CHECK(k.size(1) == p.H && k.size(2) == p.d && v.size(1) == p.H, "bad head layout");
+  TORCH_CHECK(w_pre.size(0) == r.size(0) && a_pre.size(0) == r.size(0) && w_pre.size(1) == p.H * p.d && a_pre.size(1) == p.H * p.d,
+              "decay / removal pre-activations must be [T, H * d]");
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == p.H && state.size(2) == p.d && state.size(3) == p.dv, "bad state shape");
+  TORCH_CHECK(out.numel() == r.size(0) * p.H * p.dv, "bad out shape");
+  if (w_bias.has_value() && w_bias->defined()) {
+    TORCH_CHECK(w_bias->scalar_type() == r.scalar_type() && w_bias->is_contiguous() && w_bias->numel() == p.H * p.d, "bad decay bias");
+    p.w_bias = w_bias->data_ptr();
+  }
+  p.r = r.data_ptr(); p.k = k.data_ptr(); p.v = v.data_ptr(); p.w_pre = w_pre.data_ptr(); p.a_pre = a_pre.data_ptr();
+  p.ldr = r.stride(0); p.ldk = k.stride(0); p.ldv = v.stride(0); p.ldw = w_pre.stride(0); p.lda = a_pre.stride(0);
+  p.cu = cu.data_ptr<int>(); p.rows = rows.data_ptr<int>(); p.state = state.data_ptr<float>(); p.out = out.data_ptr<float>();
+  p.decay_scale = static_cast<float>(decay_scale); p.unit_eps = static_cast<float>(unit_eps);
+  c10::cuda::CUDAGuard g(r.device());
+  TORCH_CHECK(b200seq::gen_delta_scan(p, static_cast<int>(rows.numel()), bf16, cur_stream()), "gen_delta_scan: key dim ", p.d,
+              " above the largest kernel instance (256)");
+  count(); check_last_error("gen_delta_scan");
+}
+
+void mingru_scan(const Tensor& z_pre, const Tensor& u_pre, const Tensor& g_pre, const Tensor& cu, const Tensor& rows, Tensor state, Tensor y,
+                 int64_t max_len) {
+  const bool bf16 = act_is_bf16(z_pre, "z_pre");
+  check_act2(z_pre, z_pre, "z_pre"); check_act2(u_pre, z_pre, "u_pre"); check_act2(g_pre, z_pre, "g_pre");
+  check_f32(state, "state"); check_i32(cu, "cu"); check_i32(rows, "rows");
+  b200seq::MinGruArgs p{};
+  p.C = static_cast<int>(z_pre.size(1));
+  TORCH_CHECK(u_pre.sizes() == z_pre.sizes() && g_pre.sizes() == z_pre.sizes() && state.dim() == 2 && state.size(1) == p.C, "bad shapes");
+  TORCH_CHECK(y.scalar_type() == z_pre.scalar_type() && y.is_contiguous() && y.sizes() == z_pre.sizes(), "bad y");
+  p.z_pre = z_pre.data_ptr(); p.u_pre = u_pre.data_ptr(); p.g_pre = g_pre.data_ptr();
+  p.ldz = z_pre.stride(0); p.ldu = u_pre.stride(0); p.ldg = g_pre.stride(0);
+  p.cu = cu.data_ptr<int>(); p.rows = rows.data_ptr<int>(); p.state = state.data_ptr<float>(); p.y = y.data_ptr();
+  c10::cuda::CUDAGuard g(z_pre.device());
+  const int R = static_cast<int>(rows.numel());
+  p.max_runs = b200seq::mingru_runs(static_cast<int>(max_len));
+  Tensor ws;
+  if (p.max_runs > 1) {
+    ws = torch::empty({R, p.max_runs, p.C, 2}, state.options());
+    p.ws = ws.data_ptr<float>();
+  }
+  b200seq::mingru_scan(p, R, bf16, cur_stream());
+  count(p.max_runs > 1 ? 3 : 1); check_last_error("mingru_scan");
+}
+
+void clamped_glu(const Tensor& x, Tensor y, double limit, double alpha, double shift) {
+  const bool bf16 = act_is_bf16(x, "x");
+  check_act2(x, x, "x");
+  TORCH_CHECK(x.size(1) % 2 == 0 && y.scalar_type() == x.scalar_type() && y.is_contiguous() && y.dim() == 2 && y.size(0) == x.size(0) &&
+              y.size(1) * 2 == x.size(1), "x must be [T, 2 F], y [T, F]");
+  c10::cuda::CUDAGuard g(x.device());
+  b200seq::clamped_glu(x.data_ptr(), x.stride(0), y.data_ptr(), x.size(0), static_cast<int>(y.size(1)), static_cast<float>(limit),
+                       static_cast<float>(alpha), static_cast<float>(shift), bf16, cur_stream());
+  count(); check_last_error("clamped_glu");
+}
+
 }  // namespace
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("add_rms_norm", &add_rms_norm);
   m.def("gated_head_rms_norm", &gated_head_rms_norm);
-  m.def("causal_conv_silu", &causal_conv_silu);
+  m.def("causal_conv", &causal_conv);
   m.def("delta_rule_scan", &delta_rule_scan);
   m.def("mlstm_scan", &mlstm_scan);
   m.def("latent_attention_paged", &latent_attention_paged);
   m.def("group_limited_router", &group_limited_router);
+  m.def("norm_add", &norm_add);
+  m.def("norm_rope", &norm_rope);
+  m.def("mixed_attention_paged", &mixed_attention_paged);
+  m.def("gen_delta_scan", &gen_delta_scan);
+  m.def("mingru_scan", &mingru_scan);
+  m.def("clamped_glu", &clamped_glu);
   m.def("launch_count", []() { return g_launches.load(); });
   m.def("reset_launch_count", []() { g_launches.store(0); });
 }

@@ -10,37 +10,21 @@
 #include <stdint.h>
 #include <algorithm>
 
+#include "seq_common.cuh"
 #include "seqmix_api.h"
 
 namespace b200seq {
 
 namespace {
 
-template <typename T> __device__ __forceinline__ float ld(const T* p);
-template <> __device__ __forceinline__ float ld<float>(const float* p) { return *p; }
-template <> __device__ __forceinline__ float ld<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
-template <typename T> __device__ __forceinline__ void st(T* p, float v);
-template <> __device__ __forceinline__ void st<float>(float* p, float v) { *p = v; }
-template <> __device__ __forceinline__ void st<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
-
-__device__ __forceinline__ float warp_sum(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-  return v;
-}
-__device__ __forceinline__ float warp_max(float v) {
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
-  return v;
-}
-__device__ __forceinline__ float sigmoidf_(float x) { return 1.0f / (1.0f + expf(-x)); }
+using namespace dev;
 
 // ---------------------------------------------------------------------------------------------------------------------
-// x (fp32, in place) += delta ; y = x * rsqrt(mean(x^2) + eps) * w
+// x (fp32, in place) += delta ; y = x * rsqrt(mean(x^2) + eps) * (w_off + w)
 // ---------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void __launch_bounds__(256) add_rms_norm_kernel(float* __restrict__ x, const T* __restrict__ delta,
-                                                           const T* __restrict__ w, T* __restrict__ y, int cols, float eps) {
+                                                           const T* __restrict__ w, T* __restrict__ y, int cols, float eps, float w_off) {
   extern __shared__ float row[];
   __shared__ float red[8];
   const int64_t base = static_cast<int64_t>(blockIdx.x) * cols;
@@ -60,7 +44,7 @@ __global__ void __launch_bounds__(256) add_rms_norm_kernel(float* __restrict__ x
   float tot = 0.f;
   for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
   const float r = 1.0f / sqrtf(tot / static_cast<float>(cols) + eps);
-  for (int c = threadIdx.x; c < cols; c += blockDim.x) st(y + base + c, row[c] * r * ld(w + c));
+  for (int c = threadIdx.x; c < cols; c += blockDim.x) st(y + base + c, row[c] * r * (w_off + ld(w + c)));
 }
 
 // one warp per (token, head): o / rms(o) * w * sigmoid(gate)
@@ -83,12 +67,12 @@ __global__ void gated_head_rms_norm_kernel(const float* __restrict__ o, const T*
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// depth-wise causal convolution + SiLU; the window holds the taps - 1 inputs that preceded the step
+// depth-wise causal convolution (+ SiLU when asked for); the window holds the taps - 1 inputs that preceded the step
 // ---------------------------------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w, const int* __restrict__ cu,
                                         const int* __restrict__ rows, const int* __restrict__ tok_seq, const T* __restrict__ window,
-                                        T* __restrict__ y, int n_tok, int C, int taps) {
+                                        T* __restrict__ y, int n_tok, int C, int taps, int silu) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
   if (idx >= static_cast<int64_t>(n_tok) * C) return;
   const int t = static_cast<int>(idx / C), c = static_cast<int>(idx % C);
@@ -100,7 +84,7 @@ __global__ void causal_conv_silu_kernel(const T* __restrict__ x, int64_t ldx, co
     const float in = src >= a ? ld(x + src * ldx + c) : ld(win + static_cast<int64_t>(taps - 1 + (src - a)) * C + c);
     acc += ld(w + static_cast<int64_t>(c) * taps + j) * in;
   }
-  st(y + static_cast<int64_t>(t) * C + c, acc * sigmoidf_(acc));
+  st(y + static_cast<int64_t>(t) * C + c, silu ? acc * sigmoidf_(acc) : acc);
 }
 
 // Two adjacent channels and a run of kConvRun tokens of one sequence per thread: every input is read once and slides through
@@ -124,7 +108,7 @@ template <> struct Pair<__nv_bfloat16> {
 template <typename T, int TAPS>
 __global__ void __launch_bounds__(128) causal_conv_silu_run_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w,
                                                                    const int* __restrict__ cu, const int* __restrict__ rows,
-                                                                   const T* __restrict__ window, T* __restrict__ y, int C) {
+                                                                   const T* __restrict__ window, T* __restrict__ y, int C, int silu) {
   const int c = 2 * (blockIdx.x * blockDim.x + threadIdx.x), r = blockIdx.z;
   const int a = cu[r], b = cu[r + 1];
   const int t_lo = a + blockIdx.y * kConvRun, t_hi = min(b, t_lo + kConvRun);
@@ -143,7 +127,8 @@ __global__ void __launch_bounds__(128) causal_conv_silu_run_kernel(const T* __re
     float2 acc = make_float2(0.f, 0.f);
 #pragma unroll
     for (int j = 0; j < TAPS; ++j) { acc.x = fmaf(wt[j].x, hist[j].x, acc.x); acc.y = fmaf(wt[j].y, hist[j].y, acc.y); }
-    Pair<T>::store(y + static_cast<int64_t>(t) * C + c, make_float2(acc.x * sigmoidf_(acc.x), acc.y * sigmoidf_(acc.y)));
+    if (silu) acc = make_float2(acc.x * sigmoidf_(acc.x), acc.y * sigmoidf_(acc.y));
+    Pair<T>::store(y + static_cast<int64_t>(t) * C + c, acc);
 #pragma unroll
     for (int j = 0; j < TAPS - 1; ++j) hist[j] = hist[j + 1];
   }
@@ -683,10 +668,11 @@ __global__ void group_limited_router_kernel(const float* __restrict__ logits, fl
   if (is_bf16) { using T = __nv_bfloat16; __VA_ARGS__; }  \
   else { using T = float; __VA_ARGS__; }
 
-void add_rms_norm(float* x, const void* delta, const void* w, void* y, int rows, int cols, float eps, bool bf16, cudaStream_t s) {
+void add_rms_norm(float* x, const void* delta, const void* w, void* y, int rows, int cols, float eps, float w_off, bool bf16,
+                  cudaStream_t s) {
   if (rows == 0) return;
   SEQ_DISPATCH_T(bf16, add_rms_norm_kernel<T><<<rows, 256, cols * sizeof(float), s>>>(
-                           x, static_cast<const T*>(delta), static_cast<const T*>(w), static_cast<T*>(y), cols, eps));
+                           x, static_cast<const T*>(delta), static_cast<const T*>(w), static_cast<T*>(y), cols, eps, w_off));
 }
 
 void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* y, int n_tok, int H, int dv, bool w_per_head,
@@ -700,15 +686,16 @@ void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* 
 
 template <typename T, int TAPS>
 static void launch_conv_run(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const void* window, void* y,
-                            int R, int C, int max_len, cudaStream_t s) {
+                            int R, int C, int max_len, int silu, cudaStream_t s) {
   dim3 grid((C / 2 + 127) / 128, (max_len + kConvRun - 1) / kConvRun, R);
   causal_conv_silu_run_kernel<T, TAPS><<<grid, 128, 0, s>>>(static_cast<const T*>(x), ldx, static_cast<const T*>(w), cu, rows,
-                                                            static_cast<const T*>(window), static_cast<T*>(y), C);
+                                                            static_cast<const T*>(window), static_cast<T*>(y), C, silu);
 }
 
 void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const int* tok_seq, void* window,
-                      void* y, int n_tok, int R, int C, int taps, int max_len, bool bf16, cudaStream_t s) {
+                      void* y, int n_tok, int R, int C, int taps, int max_len, bool silu, bool bf16, cudaStream_t s) {
   if (n_tok == 0) return;
+  const int act = silu ? 1 : 0;
   const int64_t n = static_cast<int64_t>(n_tok) * C;
   // the paired kernel needs even channel counts and strides, 4- / 8-byte aligned bases, and a grid within the launch limits
   const size_t pair_bytes = bf16 ? 4 : 8;
@@ -716,12 +703,12 @@ void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, 
                       reinterpret_cast<uintptr_t>(y) % pair_bytes == 0 && reinterpret_cast<uintptr_t>(window) % pair_bytes == 0 &&
                       max_len > 0 && (max_len + kConvRun - 1) / kConvRun <= 65535 && R <= 65535;
   SEQ_DISPATCH_T(bf16, {
-    if (paired && taps == 2) launch_conv_run<T, 2>(x, ldx, w, cu, rows, window, y, R, C, max_len, s);
-    else if (paired && taps == 3) launch_conv_run<T, 3>(x, ldx, w, cu, rows, window, y, R, C, max_len, s);
-    else if (paired && taps == 4) launch_conv_run<T, 4>(x, ldx, w, cu, rows, window, y, R, C, max_len, s);
+    if (paired && taps == 2) launch_conv_run<T, 2>(x, ldx, w, cu, rows, window, y, R, C, max_len, act, s);
+    else if (paired && taps == 3) launch_conv_run<T, 3>(x, ldx, w, cu, rows, window, y, R, C, max_len, act, s);
+    else if (paired && taps == 4) launch_conv_run<T, 4>(x, ldx, w, cu, rows, window, y, R, C, max_len, act, s);
     else causal_conv_silu_kernel<T><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
         static_cast<const T*>(x), ldx, static_cast<const T*>(w), cu, rows, tok_seq, static_cast<const T*>(window),
-        static_cast<T*>(y), n_tok, C, taps);
+        static_cast<T*>(y), n_tok, C, taps, act);
     if (taps > 1)
       conv_window_update_kernel<T><<<(R * C + 255) / 256, 256, 0, s>>>(static_cast<const T*>(x), ldx, cu, rows,
                                                                         static_cast<T*>(window), R, C, taps);

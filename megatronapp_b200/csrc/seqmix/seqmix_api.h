@@ -1,4 +1,4 @@
-// Host API of the sequence-mixing kernels (see seqmix.cu).  Pointers are device pointers; `bf16` selects the activation type
+// Host API of the sequence-mixing kernels (see seqmix.cu and seqmix_parallel.cu).  Pointers are device pointers; `bf16` selects the activation type
 // (__nv_bfloat16, else float).  Functions returning bool report false for sizes no kernel instance covers.
 #pragma once
 #include <cuda_runtime.h>
@@ -42,11 +42,11 @@ struct LatentAttnArgs {
   float scale;
 };
 
-void add_rms_norm(float* x, const void* delta, const void* w, void* y, int rows, int cols, float eps, bool bf16, cudaStream_t s);
+void add_rms_norm(float* x, const void* delta, const void* w, void* y, int rows, int cols, float eps, float w_off, bool bf16, cudaStream_t s);
 void gated_head_rms_norm(const float* o, const void* w, const void* gate, void* y, int n_tok, int H, int dv, bool w_per_head,
                          float eps, bool bf16, cudaStream_t s);
 void causal_conv_silu(const void* x, int64_t ldx, const void* w, const int* cu, const int* rows, const int* tok_seq, void* window,
-                      void* y, int n_tok, int R, int C, int taps, int max_len, bool bf16, cudaStream_t s);
+                      void* y, int n_tok, int R, int C, int taps, int max_len, bool silu, bool bf16, cudaStream_t s);
 bool delta_rule_scan(const DeltaArgs& p, int R, bool bf16, cudaStream_t s);
 bool mlstm_scan(const MlstmArgs& p, int R, bool bf16, cudaStream_t s);
 bool latent_attention_paged(const LatentAttnArgs& p, int n_tok, bool bf16, cudaStream_t s);
@@ -54,5 +54,65 @@ bool latent_attention_paged(const LatentAttnArgs& p, int n_tok, bool bf16, cudaS
 int latent_attention_splits(int H, int r, int n_tok, int max_len);
 bool group_limited_router(const float* logits, float* probs, bool* rmap, int n_tok, int E, int topk, int G, int keep, bool renorm,
                           cudaStream_t s);
+
+struct NormRopeArgs {
+  const void *q, *k;              // [T, q_ch], [T, k_ch] with row strides ldq / ldk (elements)
+  int64_t ldq, ldk;
+  const void *wq, *wk;            // norm weights over the whole projection
+  const int64_t* positions;       // [T]
+  const float* inv_freq;          // [rot / 2]
+  void *q_out, *k_out;            // contiguous [T, q_ch], [T, k_ch]
+  int q_ch, k_ch, head_dim, rot;
+  float eps;
+};
+
+struct MixAttnArgs {
+  const void* q;                  // [T, H, d], row stride ldq
+  int64_t ldq;
+  const void *kcache, *vcache;    // [slots, G, d], [slots, G, dv]
+  const int *block_table, *tok_req, *tok_len;
+  const float* talk;              // [H, H] mixing matrix (nullptr: none)
+  const void* gate;               // [T, H * dv] pre-activation of the output gate, row stride ldg (nullptr: none)
+  int64_t ldg;
+  void* out;                      // [T, H * dv]
+  float* ws_stats;                // [T, n_splits, H, 2] when n_splits > 1
+  float* ws_acc;                  // [T, n_splits, H * dv] when n_splits > 1
+  int H, G, d, dv, block_size, max_blocks, n_splits;
+  int key_tile, head_words, ldk_s;  // filled by the launcher
+  float scale;
+};
+
+struct GenDeltaArgs {
+  const void *r, *k, *v;          // [T, H, d], [T, H, d], [T, H, dv] with row strides
+  const void *w_pre, *a_pre;      // [T, H * d] pre-activations of decay and removal rate, row strides ldw / lda
+  const void* w_bias;             // [H * d] added to w_pre (nullptr: none)
+  int64_t ldr, ldk, ldv, ldw, lda;
+  const int *cu, *rows;
+  float* state;                   // [rows, H, d, dv]
+  float* out;                     // [T, H, dv]
+  int H, d, dv;
+  float decay_scale, unit_eps;
+};
+
+struct MinGruArgs {
+  const void *z_pre, *u_pre, *g_pre;   // [T, C] with row strides
+  int64_t ldz, ldu, ldg;
+  const int *cu, *rows;
+  float* state;                   // [rows, C]
+  void* y;                        // [T, C]
+  float* ws;                      // [R, max_runs, C, 2] when max_runs > 1
+  int C, max_runs;
+};
+
+void norm_add(float* x, const void* a, const void* b, const void* wa, const void* wb, const void* w, void* y, int rows, int cols,
+              float eps, float w_off, bool bf16, cudaStream_t s);
+void norm_rope(const NormRopeArgs& p, int n_tok, bool bf16, cudaStream_t s);
+int mixed_attention_splits(int n_tok, int max_len);
+bool mixed_attention_paged(const MixAttnArgs& p, int n_tok, bool bf16, cudaStream_t s);
+bool gen_delta_scan(const GenDeltaArgs& p, int R, bool bf16, cudaStream_t s);
+int mingru_runs(int max_len);
+void mingru_scan(const MinGruArgs& p, int R, bool bf16, cudaStream_t s);
+void clamped_glu(const void* x, int64_t ldx, void* y, int64_t n_tok, int F, float limit, float alpha, float shift, bool bf16,
+                 cudaStream_t s);
 
 }  // namespace b200seq

@@ -11,7 +11,8 @@ blocks, a token at position ``p`` lives in slot ``table[p // bs] * bs + p % bs``
 request's slots (padded over requests), so admission, retirement and preemption never move KV data.
 
 Layers need not be softmax attention with their own K/V.  Latent-attention layers page one latent vector per token
-(``attend_latent``), and a layer may read the pages another layer wrote.  Recurrent mixers keep a fixed-size state per
+(``attend_latent``), and a layer may read the pages another layer wrote; ``attend_mixed`` serves attention whose
+softmax weights are mixed across heads.  Recurrent mixers keep a fixed-size state per
 request instead of pages: every request owns a *state row* for its lifetime (``recurrent_state`` hands out per-layer
 tensors ``[max_requests, ...]`` indexed by that row, zeroed when the row is given to a new request), and ``packed``
 describes the step's sequence boundaries and rows to the scan kernels.  Chunked prefill, continuous batching and
@@ -225,6 +226,24 @@ class DynamicInferenceContext:
         self.kernel_calls += 1
         return seqmix.latent_attention_paged(q_lat, self.latents[layer], self._block_table, self._tok_req, self._tok_len,
                                              self.block_size, scale, self._max_len)
+
+    def attend_mixed(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float,
+                     talk: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Grouped-query attention whose softmax weights are mixed across heads (``talk [H, H]``), over the pages of cache
+        ``layer``: ``q [T, H, d]``, new ``k [T, G, d]`` / ``v [T, G, dv]`` (written into their pages first), optional output
+        gate ``[T, H * dv]`` (pre-activation) -> ``[T, H * dv]``.  fp32 and 16-bit caches, any head sizes."""
+        from ..ops import seqmix
+
+        if layer not in self.kv:
+            n_slots = self.num_blocks * self.block_size
+            self.kv[layer] = (torch.zeros(n_slots, *k.shape[1:], dtype=k.dtype, device=k.device),
+                              torch.zeros(n_slots, *v.shape[1:], dtype=v.dtype, device=v.device))
+        kc, vc = self.kv[layer]
+        kc[self._write_slots] = k
+        vc[self._write_slots] = v
+        self.kernel_calls += 1
+        return seqmix.mixed_attention_paged(q, kc, vc, self._block_table, self._tok_req, self._tok_len, self.block_size, scale,
+                                            talk, gate, self._max_len)
 
     # -- attention over the paged cache --------------------------------------------
     def attend(self, layer: int, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float) -> torch.Tensor:

@@ -14,6 +14,7 @@ from typing import Optional
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
 
 from ...parallel import state as ps
 from ...parallel.mappings import scatter_to_sequence_parallel_region
@@ -80,6 +81,58 @@ class LanguageModelEmbedding(MegatronModule):
         else:
             emb = self.embedding_dropout(emb)
         return emb
+
+
+class HashedBigramEmbedding(MegatronModule):
+    """An embedding of the (previous token, token) pair, hashed into a table: row
+    ``(prev * mul_prev + token * mul_cur) mod buckets``; a sequence's first token, which has no predecessor, reads the
+    extra row ``buckets`` at the table's end.  Its output is added to the word embedding.
+
+    The previous token is part of a sequence's state: under the dynamic engine the last token of every step is kept in
+    the context's per-request state (stored plus one, so that the zero of a fresh row means "none"), and a step that
+    continues a sequence -- a later portion of a prompt or a decoded token -- pairs its first token with it."""
+
+    def __init__(self, config, buckets: int, mul_prev: int, mul_cur: int):
+        super().__init__(config)
+        self.buckets, self.mul_prev, self.mul_cur = int(buckets), int(mul_prev), int(mul_cur)
+        dev = "cpu" if (config.use_cpu_initialization or not torch.cuda.is_available()) else torch.cuda.current_device()
+        self.weight = nn.Parameter(torch.zeros(self.buckets + 1, config.hidden_size, dtype=config.params_dtype, device=dev))
+        if config.perform_initialization:
+            config.init_method(self.weight)
+
+    def rows(self, ids: torch.Tensor, prev: torch.Tensor) -> torch.Tensor:
+        """Table rows for tokens ``ids`` after ``prev`` (``-1``: no predecessor); int64 tensors of one shape."""
+        row = (prev * self.mul_prev + ids * self.mul_cur) % self.buckets
+        return torch.where(prev < 0, torch.full_like(row, self.buckets), row)
+
+    def forward(self, input_ids: torch.Tensor, inference_context=None) -> torch.Tensor:
+        """``input_ids [b, s]`` -> ``[s, b, h]``.  With a dynamic context ``input_ids`` is the packed batch ``[1, T]``."""
+        ids = input_ids.long()
+        if inference_context is not None and not inference_context.is_static_batching():
+            pb = inference_context.packed
+            state = inference_context.recurrent_state(("bigram.prev",), (), torch.int64)
+            flat = ids[0]
+            cu, slots = pb.cu.long(), pb.slots.long()
+            prev = torch.roll(flat, 1)
+            prev[cu[:-1]] = state[slots] - 1
+            state[slots] = flat[cu[1:] - 1] + 1
+            return F.embedding(self.rows(flat, prev), self.weight).unsqueeze(1)
+        if inference_context is not None:
+            raise NotImplementedError("the bigram embedding serves through the dynamic engine")
+        prev = torch.roll(ids, 1, dims=1)
+        prev[:, 0] = -1
+        return F.embedding(self.rows(ids, prev), self.weight).transpose(0, 1).contiguous()
+
+
+def llama3_scaled_frequencies(dims: int, base: float, scaling: Optional[dict] = None) -> torch.Tensor:
+    """Rotary frequencies ``base^(-2i / dims)``, ``i < dims / 2``, as fp32 (computed in fp64).  ``scaling`` (``factor``,
+    ``low``, ``high``, ``original``) applies the wavelength-dependent rule of ``_apply_llama3_scaling``: short wavelengths
+    keep their frequency, long ones are divided by ``factor``, those between are interpolated."""
+    f = float(base) ** (-torch.arange(0, dims, 2, dtype=torch.float64) / dims)
+    if scaling:
+        f = _apply_llama3_scaling(f, float(scaling["factor"]), float(scaling["low"]), float(scaling["high"]),
+                                  float(scaling["original"]))
+    return f.to(torch.float32)
 
 
 def _apply_llama3_scaling(inv_freq, factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0, original_max=8192):

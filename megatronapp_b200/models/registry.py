@@ -50,6 +50,13 @@ def _zikunex(path, params_dtype, device, **overrides):
     return load_model_dir(path, params_dtype, device, **overrides)
 
 
+@register_architecture("Lerorax")
+def _lerorax(path, params_dtype, device, **overrides):
+    from .lerorax.loader import load_model_dir
+
+    return load_model_dir(path, params_dtype, device, **overrides)
+
+
 @register_architecture("GPTModel")
 def _gpt(path, params_dtype, device, **overrides):
     """A GPT / Llama-style folder: ``config.json`` holds ``TransformerConfig`` fields under ``transformer`` plus

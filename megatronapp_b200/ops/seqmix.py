@@ -96,17 +96,18 @@ class PackedBatch:
 # ---------------------------------------------------------------------------
 
 def add_rms_norm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
-                 out_dtype: torch.dtype) -> Tuple[torch.Tensor, torch.Tensor]:
-    """``x`` fp32 ``[T, h]`` (updated in place by ``+ delta`` when given) -> ``(x, rms_norm(x) * weight)``; the
-    normalised copy leaves in ``out_dtype``, the statistics are fp32."""
+                 out_dtype: torch.dtype, weight_offset: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``x`` fp32 ``[T, h]`` (updated in place by ``+ delta`` when given) -> ``(x, rms_norm(x) * (weight_offset + weight))``;
+    the normalised copy leaves in ``out_dtype``, the statistics are fp32.  ``weight_offset = 1`` is a weight stored around
+    zero."""
     if x.is_cuda:
         kernel_calls["add_rms_norm"] += 1
         y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
-        ext().add_rms_norm(x, delta if delta is None else delta.contiguous(), weight, y, float(eps))
+        ext().add_rms_norm(x, delta if delta is None else delta.contiguous(), weight, y, float(eps), float(weight_offset))
         return x, y
     if delta is not None:
         x.add_(delta.float())
-    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.float()
+    y = x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * (weight.float() + weight_offset)
     return x, y.to(out_dtype)
 
 
@@ -134,14 +135,19 @@ def gated_head_rms_norm(o: torch.Tensor, weight: torch.Tensor, gate: Optional[to
 # ---------------------------------------------------------------------------
 
 def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: torch.Tensor) -> torch.Tensor:
-    """Depth-wise causal convolution over time followed by SiLU.  ``x [T, C]``, ``weight [C, taps]`` (last column
-    multiplies the current token), ``window [rows, taps - 1, C]``: the inputs that preceded each sequence's first token
-    of this step (zeros at a sequence's start); on return it holds the last ``taps - 1`` inputs seen."""
+    """``causal_conv`` followed by SiLU."""
+    return causal_conv(x, weight, pb, window, silu=True)
+
+
+def causal_conv(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, window: torch.Tensor, silu: bool = False) -> torch.Tensor:
+    """Depth-wise causal convolution over time, optionally followed by SiLU.  ``x [T, C]``, ``weight [C, taps]`` (last
+    column multiplies the current token), ``window [rows, taps - 1, C]``: the inputs that preceded each sequence's first
+    token of this step (zeros at a sequence's start); on return it holds the last ``taps - 1`` inputs seen."""
     if x.is_cuda:
-        kernel_calls["causal_conv_silu"] += 1
+        kernel_calls["causal_conv_silu" if silu else "causal_conv"] += 1
         y = torch.empty(x.shape, dtype=x.dtype, device=x.device)
-        ext().causal_conv_silu(x if x.stride(1) == 1 else x.contiguous(), weight.contiguous(), pb.cu, pb.slots, pb.tok_seq,
-                               window, y, pb.max_len)
+        ext().causal_conv(x if x.stride(1) == 1 else x.contiguous(), weight.contiguous(), pb.cu, pb.slots, pb.tok_seq,
+                          window, y, pb.max_len, bool(silu))
         return y
     taps = weight.shape[1]
     w = weight.float()
@@ -152,7 +158,7 @@ def causal_conv_silu(x: torch.Tensor, weight: torch.Tensor, pb: PackedBatch, win
             continue
         seq = torch.cat([window[s].float(), x[a:b].float()], dim=0)                # [taps - 1 + n, C]
         y = sum(seq[j:j + (b - a)] * w[:, j] for j in range(taps))
-        out.append(F.silu(y))
+        out.append(F.silu(y) if silu else y)
         if taps > 1:
             window[s] = seq[-(taps - 1):].to(window.dtype)
     return torch.cat(out, dim=0).to(x.dtype)
@@ -306,3 +312,194 @@ def group_limited_router(logits: torch.Tensor, topk: int, num_groups: int, keep_
     if renormalize:
         w = w / (w.sum(-1, keepdim=True) + 1e-20)
     return torch.zeros_like(s).scatter_(1, idx, w), torch.zeros(T, E, dtype=torch.bool).scatter_(1, idx, True)
+
+
+# ---------------------------------------------------------------------------
+# norm on a sublayer's output, fused with the fp32 residual addition
+# ---------------------------------------------------------------------------
+
+def _rms(t: torch.Tensor, eps: float) -> torch.Tensor:
+    return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + eps)
+
+
+def norm_add(x: torch.Tensor, a: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype,
+             weight_offset: float = 0.0, b: Optional[torch.Tensor] = None, weight_a: Optional[torch.Tensor] = None,
+             weight_b: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``x`` fp32 ``[T, h]`` is updated in place by ``+ rms_norm(m) * (weight_offset + weight)`` and returned with a copy in
+    ``out_dtype``.  ``m`` is the sublayer output ``a``; with a second branch ``b`` it is the mean of the two branches, each
+    RMS-normed with its own plain weight: ``(rms_norm(a) * weight_a + rms_norm(b) * weight_b) / 2``."""
+    if x.is_cuda:
+        kernel_calls["norm_add"] += 1
+        y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+        ext().norm_add(x, a.contiguous(), None if b is None else b.contiguous(), weight_a, weight_b, weight, y, float(eps),
+                       float(weight_offset))
+        return x, y
+    m = a.float()
+    if b is not None:
+        m = 0.5 * (_rms(m, eps) * weight_a.float() + _rms(b.float(), eps) * weight_b.float())
+    x.add_(_rms(m, eps) * (weight.float() + weight_offset))
+    return x, x.to(out_dtype)
+
+
+# ---------------------------------------------------------------------------
+# whole-projection q / k norm + partial interleaved rotary positions
+# ---------------------------------------------------------------------------
+
+def norm_rope(q: torch.Tensor, k: torch.Tensor, weight_q: torch.Tensor, weight_k: torch.Tensor, positions: torch.Tensor,
+              inv_freq: torch.Tensor, head_dim: int, rot_dims: int, eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """``q [T, H * d]`` and ``k [T, G * d]`` (column slices of a fused projection are fine): each is RMS-normed over its
+    whole row with a weight per channel, then the first ``rot_dims`` dimensions of every head are rotated, dimension
+    ``2i`` paired with ``2i + 1``, by the angle ``positions[t] * inv_freq[i]`` (fp32).  Returns contiguous ``(q, k)``."""
+    if q.is_cuda:
+        kernel_calls["norm_rope"] += 1
+        qo = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+        ko = torch.empty(k.shape, dtype=k.dtype, device=k.device)
+        ext().norm_rope(q if q.stride(1) == 1 else q.contiguous(), k if k.stride(1) == 1 else k.contiguous(), weight_q, weight_k,
+                        positions.contiguous(), inv_freq, qo, ko, int(head_dim), int(rot_dims), float(eps))
+        return qo, ko
+    ang = positions.float().unsqueeze(-1) * inv_freq.float()                          # [T, rot / 2]
+    cs, sn = torch.cos(ang).unsqueeze(1), torch.sin(ang).unsqueeze(1)
+    outs = []
+    for t, w in ((q, weight_q), (k, weight_k)):
+        y = (_rms(t.float(), eps) * w.float()).view(t.shape[0], -1, head_dim).clone()
+        u, v = y[..., 0:rot_dims:2].clone(), y[..., 1:rot_dims:2].clone()
+        y[..., 0:rot_dims:2] = u * cs - v * sn
+        y[..., 1:rot_dims:2] = v * cs + u * sn
+        outs.append(y.view(t.shape).to(t.dtype))
+    return outs[0], outs[1]
+
+
+# ---------------------------------------------------------------------------
+# paged grouped-query attention whose softmax weights are mixed across heads
+# ---------------------------------------------------------------------------
+
+def mixed_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
+                          tok_req: torch.Tensor, tok_len: torch.Tensor, block_size: int, scale: float,
+                          talk: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, max_len: int = 0) -> torch.Tensor:
+    """``q [T, H, d]`` against paged keys ``[slots, G, d]`` and values ``[slots, G, dv]``: per head the ordinary softmax
+    over the ``tok_len[t]`` visible keys of the token's sequence; the weights of all heads are then mixed,
+    ``M_h = sum_g talk[h, g] P_g`` (``talk`` fp32 ``[H, H]``; ``None``: no mixing), and head ``h`` applies ``M_h`` to the
+    values of its own key/value head ``h // (H / G)``.  ``gate [T, H * dv]`` (pre-activation) multiplies the result by
+    its sigmoid.  Scores, weights and sums are fp32.  Returns ``[T, H * dv]`` in ``q``'s dtype."""
+    T, H, d = q.shape
+    G, dv = kcache.shape[1], vcache.shape[2]
+    if q.is_cuda:
+        kernel_calls["mixed_attention_paged"] += 1
+        o = torch.empty(T, H * dv, dtype=q.dtype, device=q.device)
+        ext().mixed_attention_paged(_rows3(q), kcache, vcache, block_table, tok_req, tok_len,
+                                    None if talk is None else talk.float().contiguous(),
+                                    None if gate is None else (gate if gate.stride(1) == 1 else gate.contiguous()), o,
+                                    int(block_size), float(scale), int(max_len))
+        return o
+    o = torch.empty(T, H, dv, dtype=torch.float32)
+    req, lens = tok_req.tolist(), tok_len.tolist()
+    rep = H // G
+    t = 0
+    while t < T:
+        e = t
+        while e + 1 < T and req[e + 1] == req[t]:
+            e += 1
+        L = max(lens[t:e + 1])
+        pos = torch.arange(L)
+        slots = block_table[req[t]].long()[pos // block_size] * block_size + pos % block_size
+        kk = kcache[slots].float().repeat_interleave(rep, dim=1)                        # [L, H, d]
+        vv = vcache[slots].float().repeat_interleave(rep, dim=1)
+        s = torch.einsum("thd,lhd->htl", q[t:e + 1].float(), kk) * scale
+        vis = pos.view(1, 1, L) < torch.tensor(lens[t:e + 1]).view(1, -1, 1)
+        P = torch.softmax(s.masked_fill(~vis, float("-inf")), -1)
+        if talk is not None:
+            P = torch.einsum("hg,gtl->htl", talk.float(), P)
+        o[t:e + 1] = torch.einsum("htl,lhv->thv", P, vv)
+        t = e + 1
+    o = o.reshape(T, H * dv)
+    if gate is not None:
+        o = o * torch.sigmoid(gate.float())
+    return o.to(q.dtype)
+
+
+# ---------------------------------------------------------------------------
+# generalized delta rule: per-channel decay and removal along the unit key
+# ---------------------------------------------------------------------------
+
+def gen_delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w_pre: torch.Tensor, a_pre: torch.Tensor,
+                   w_bias: Optional[torch.Tensor], pb: PackedBatch, state: torch.Tensor, decay_scale: float,
+                   unit_eps: float = 1e-6) -> torch.Tensor:
+    """``r, k [T, H, d]``, ``v [T, H, dv]``, pre-activations ``w_pre, a_pre [T, H * d]``, ``state [rows, H, d, dv]`` fp32
+    -> ``o [T, H, dv]`` fp32.  Per head and token, with ``u = k / sqrt(sum k^2 + unit_eps)``::
+
+        w = exp(-decay_scale * sigmoid(w_pre + w_bias));  a = sigmoid(a_pre)
+        S <- diag(w) S - (a * u) (u^T S) + k v^T   (both terms read the old S);   o = S^T r
+    """
+    T, H, dv = v.shape
+    d = r.shape[2]
+    if r.is_cuda:
+        kernel_calls["gen_delta_scan"] += 1
+        o = torch.empty(T, H, dv, dtype=torch.float32, device=r.device)
+        ext().gen_delta_scan(_rows3(r), _rows3(k), _rows3(v), w_pre if w_pre.stride(1) == 1 else w_pre.contiguous(),
+                             a_pre if a_pre.stride(1) == 1 else a_pre.contiguous(), w_bias, pb.cu, pb.slots, state, o,
+                             float(decay_scale), float(unit_eps))
+        return o
+    rf, kf, vf = r.float(), k.float(), v.float()
+    wz = w_pre.float() + (w_bias.float() if w_bias is not None else 0.0)
+    w = torch.exp(-decay_scale * torch.sigmoid(wz)).view(T, H, d)
+    a = torch.sigmoid(a_pre.float()).view(T, H, d)
+    u = kf * torch.rsqrt(kf.pow(2).sum(-1, keepdim=True) + unit_eps)
+    au = a * u
+    o = torch.empty(T, H, dv, dtype=torch.float32)
+    for s_ in range(pb.num_seqs):
+        lo, hi, row = pb.cu_host[s_], pb.cu_host[s_ + 1], pb.slots_host[s_]
+        S = state[row].clone()
+        for t in range(lo, hi):
+            proj = torch.einsum("hd,hdv->hv", u[t], S)
+            S = w[t].unsqueeze(-1) * S - au[t].unsqueeze(-1) * proj.unsqueeze(1) + kf[t].unsqueeze(-1) * vf[t].unsqueeze(1)
+            o[t] = torch.einsum("hdv,hd->hv", S, rf[t])
+        state[row] = S
+    return o
+
+
+# ---------------------------------------------------------------------------
+# minGRU
+# ---------------------------------------------------------------------------
+
+def mingru_scan(z_pre: torch.Tensor, u_pre: torch.Tensor, g_pre: torch.Tensor, pb: PackedBatch, state: torch.Tensor) -> torch.Tensor:
+    """Pre-activations ``z_pre, u_pre, g_pre [T, C]``, ``state [rows, C]`` fp32 -> ``[T, C]`` in the inputs' dtype::
+
+        z = sigmoid(z_pre);  c = u_pre + 1/2 where u_pre >= 0, sigmoid(u_pre) elsewhere
+        S <- (1 - z) S + z c;  y = S * silu(g_pre)
+    """
+    if z_pre.is_cuda:
+        kernel_calls["mingru_scan"] += 1
+        y = torch.empty(z_pre.shape, dtype=z_pre.dtype, device=z_pre.device)
+        fix = lambda t: t if t.stride(1) == 1 else t.contiguous()  # noqa: E731
+        ext().mingru_scan(fix(z_pre), fix(u_pre), fix(g_pre), pb.cu, pb.slots, state, y, pb.max_len)
+        return y
+    z, u = torch.sigmoid(z_pre.float()), u_pre.float()
+    cand = torch.where(u >= 0, u + 0.5, torch.sigmoid(u))
+    out = torch.empty(z.shape, dtype=torch.float32)
+    for s_ in range(pb.num_seqs):
+        lo, hi, row = pb.cu_host[s_], pb.cu_host[s_ + 1], pb.slots_host[s_]
+        S = state[row].clone()
+        for t in range(lo, hi):
+            S = (1 - z[t]) * S + z[t] * cand[t]
+            out[t] = S
+        state[row] = S
+    return (out * F.silu(g_pre.float())).to(z_pre.dtype)
+
+
+# ---------------------------------------------------------------------------
+# clamped gated activation
+# ---------------------------------------------------------------------------
+
+def clamped_glu(x: torch.Tensor, limit: float, alpha: float = 1.702, shift: float = 1.0) -> torch.Tensor:
+    """``x [..., 2 F]`` holding ``[gate | up]`` -> ``[..., F]``: ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``,
+    ``y = g * sigmoid(alpha * g) * (u + shift)``."""
+    F_ = x.shape[-1] // 2
+    if x.is_cuda:
+        kernel_calls["clamped_glu"] += 1
+        x2 = x.reshape(-1, x.shape[-1])
+        y = torch.empty(x2.shape[0], F_, dtype=x.dtype, device=x.device)
+        ext().clamped_glu(x2 if x2.stride(1) == 1 else x2.contiguous(), y, float(limit), float(alpha), float(shift))
+        return y.view(*x.shape[:-1], F_)
+    g = torch.clamp(x[..., :F_].float(), max=limit)
+    u = torch.clamp(x[..., F_:].float(), -limit, limit)
+    return (g * torch.sigmoid(alpha * g) * (u + shift)).to(x.dtype)

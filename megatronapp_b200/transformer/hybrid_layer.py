@@ -1,4 +1,6 @@
-"""Pre-norm layer over an fp32 residual stream with an arbitrary sequence mixer, and the block that stacks such layers.
+"""Layers over an fp32 residual stream with an arbitrary sequence mixer, and the blocks that stack them: pre-norm
+(``ResidualF32Layer`` / ``ResidualF32Block``) and norm on the sublayer's output (``OutputNormF32Layer`` /
+``OutputNormF32Block``, further down).
 
 ``x <- x + mixer(norm1(x));  x <- x + mlp(norm2(x))`` (the second half is absent for a layer without feed-forward).
 The stream ``x`` stays fp32 whatever the parameter dtype; every addition is fused into the norm that follows it
@@ -15,7 +17,7 @@ import torch.nn as nn
 
 from ..scan.tracer import scope as _scope
 from .module import MegatronModule
-from .norms import ResidualRMSNorm
+from .norms import OutputRMSNormAdd, ResidualRMSNorm
 
 
 class ResidualF32Layer(MegatronModule):
@@ -72,3 +74,70 @@ class ResidualF32Block(MegatronModule):
             return x + pending.float()
         _, h = self.final_layernorm(x, pending)
         return h
+
+
+class OutputNormF32Layer(MegatronModule):
+    """``x <- x + norm1(mixer(x));  x <- x + norm2(mlp(x))``: the sublayers read the stream itself, only their outputs are
+    normed (``OutputRMSNormAdd``, whose kernel also performs the addition and hands out the copy of ``x`` in the
+    activation dtype that the next sublayer reads).  ``cache_index`` names the cache / state a call uses, so that one
+    layer object can run at several depths of a block, each with a cache of its own."""
+
+    def __init__(self, config, layer_number: int, mixer: nn.Module, mlp: Optional[nn.Module] = None, weight_offset: float = 0.0):
+        super().__init__(config)
+        self.layer_number = layer_number
+        eps = config.layernorm_epsilon
+        self.mixer, self.mlp = mixer, mlp
+        self.mixer_norm = OutputRMSNormAdd(config, config.hidden_size, eps, weight_offset=weight_offset)
+        self.mlp_norm = OutputRMSNormAdd(config, config.hidden_size, eps, weight_offset=weight_offset) if mlp is not None else None
+        if mlp is not None and hasattr(mlp, "set_layer_number"):
+            mlp.set_layer_number(layer_number)
+
+    def forward(self, x, h, inference_context=None, cache_index=None):
+        with _scope("transformer_layer", layer=self.layer_number):
+            out, bias = self.mixer(h, inference_context=inference_context,
+                                   cache_index=self.layer_number if cache_index is None else cache_index)
+            if bias is not None:
+                out = out + bias
+            x, h = self.mixer_norm(x, out)
+            if self.mlp is not None:
+                out, bias = self.mlp(h)
+                if bias is not None:
+                    out = out + bias
+                x, h = self.mlp_norm(x, out)
+        return x, h
+
+
+class OutputNormF32Block(MegatronModule):
+    """A stack of ``OutputNormF32Layer`` runs followed by the final norm.  ``layer_builders[i](i)`` builds layer object
+    ``i``; ``runs`` lists, depth by depth, which object runs there (default: each once, in order), so a layer's weights
+    can serve several depths.  Run ``k`` uses cache / state index ``k``.  ``tap(run, residual)`` as in ``ResidualF32Block``."""
+
+    def __init__(self, config, layer_builders: List[Callable[[int], OutputNormF32Layer]], runs: Optional[List[int]] = None,
+                 post_process: bool = True, weight_offset: float = 0.0):
+        super().__init__(config)
+        self.layers = nn.ModuleList([build(i) for i, build in enumerate(layer_builders)])
+        self.runs = list(range(len(self.layers))) if runs is None else [int(r) for r in runs]
+        if any(not 0 <= r < len(self.layers) for r in self.runs):
+            raise ValueError("a run names a layer that does not exist")
+        self.final_layernorm = ResidualRMSNorm(config, config.hidden_size, config.layernorm_epsilon,
+                                               weight_offset=weight_offset) if post_process else None
+        self.input_tensor = None
+        self.tap = None
+
+    def set_input_tensor(self, t):
+        self.input_tensor = t
+
+    def forward(self, hidden_states, inference_context=None):
+        x = hidden_states if self.input_tensor is None else self.input_tensor
+        if x.dtype != torch.float32:
+            x = x.float()
+        dt = self.config.params_dtype
+        h = x if dt == torch.float32 else x.to(dt)
+        for k, r in enumerate(self.runs):
+            x, h = self.layers[r](x, h, inference_context=inference_context, cache_index=k)
+            if self.tap is not None:
+                self.tap(k, x)
+        if self.final_layernorm is None:
+            return x
+        _, y = self.final_layernorm(x, None)
+        return y

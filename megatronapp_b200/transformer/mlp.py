@@ -90,6 +90,8 @@ class MLP(MegatronModule):
     def _activation(self, x, bias):
         cfg = self.config
         if cfg.gated_linear_unit:
+            if getattr(self.activation_func, "fused_glu", False):      # the activation takes the packed [gate | up] itself
+                return self.activation_func(x if bias is None else x + bias)
             if self.activation_func in (F.silu,):
                 # Megatron packs [gate | up] along the last dim of each TP shard
                 return ops.swiglu(x, bias)
@@ -119,6 +121,29 @@ class MLP(MegatronModule):
             out, out_bias = self.linear_fc2(inter)
             scope_hooks.tik_tensor(5, self.layer_number, out)
         return out, out_bias
+
+
+class ClampedGLU:
+    """Gated activation over the packed ``[gate | up]`` output of fc1 with both halves clamped:
+    ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``, ``y = g * sigmoid(alpha * g) * (u + shift)``
+    (one sm_100a kernel, ``ops.seqmix.clamped_glu``).  Use as ``activation_func`` with ``gated_linear_unit=True``."""
+
+    fused_glu = True
+
+    def __init__(self, limit: float, alpha: float = 1.702, shift: float = 1.0):
+        self.limit, self.alpha, self.shift = float(limit), float(alpha), float(shift)
+        self.__name__ = "clamped_glu"
+
+    def __call__(self, x):
+        from ..ops import seqmix
+
+        return seqmix.clamped_glu(x, self.limit, self.alpha, self.shift)
+
+    def __eq__(self, other):
+        return isinstance(other, ClampedGLU) and (self.limit, self.alpha, self.shift) == (other.limit, other.alpha, other.shift)
+
+    def __hash__(self):
+        return hash((self.limit, self.alpha, self.shift))
 
 
 def quick_gelu(x):

@@ -73,14 +73,15 @@ class ResidualRMSNorm(nn.Module):
     ``delta`` (any dtype) into the fp32 ``x`` in place and returns ``(x, x / sqrt(mean(x^2) + eps) * weight)`` with the
     normalised copy in ``out_dtype`` (the dtype the following projections run in)."""
 
-    def __init__(self, config, hidden_size: int, eps: float = 1e-5, out_dtype=None):
+    def __init__(self, config, hidden_size: int, eps: float = 1e-5, out_dtype=None, weight_offset: float = 0.0):
         super().__init__()
         self.eps, self.hidden_size = eps, hidden_size
+        self.weight_offset = float(weight_offset)     # 1.0: the weight is stored around zero and applied as 1 + w
         dtype = config.params_dtype if config is not None else torch.float32
         self.out_dtype = out_dtype          # None: the weight's dtype at call time
         dev = "cpu" if (config is None or config.use_cpu_initialization or not torch.cuda.is_available()) \
             else torch.cuda.current_device()
-        self.weight = nn.Parameter(torch.ones(hidden_size, dtype=dtype, device=dev))
+        self.weight = nn.Parameter(torch.full((hidden_size,), 1.0 - self.weight_offset, dtype=dtype, device=dev))
         setattr(self.weight, "sequence_parallel", bool(config.sequence_parallel) if config is not None else False)
 
     def forward(self, x, delta=None):
@@ -88,5 +89,42 @@ class ResidualRMSNorm(nn.Module):
 
         shape = x.shape
         x2, y = seqmix.add_rms_norm(x.view(-1, shape[-1]), None if delta is None else delta.reshape(-1, shape[-1]),
-                                    self.weight, self.eps, self.out_dtype or self.weight.dtype)
+                                    self.weight, self.eps, self.out_dtype or self.weight.dtype, self.weight_offset)
+        return x2.view(shape), y.view(shape)
+
+
+class BranchPair:
+    """Outputs of two mixers that ran side by side on the same input, with the plain RMS-norm weight of each: the layer's
+    result is ``(rms_norm(a) * weight_a + rms_norm(b) * weight_b) / 2``, which ``OutputRMSNormAdd`` computes inside its
+    kernel."""
+
+    def __init__(self, a, b, weight_a, weight_b):
+        self.a, self.b, self.weight_a, self.weight_b = a, b, weight_a, weight_b
+
+
+class OutputRMSNormAdd(nn.Module):
+    """RMS norm of a sublayer's *output*, fused with the addition to the fp32 residual stream: ``forward(x, out)`` updates
+    ``x += rms_norm(out) * (weight_offset + weight)`` in place and returns ``(x, x in out_dtype)``, the copy the next
+    sublayer reads.  ``out`` may be a ``BranchPair``.  Statistics and the sum are fp32."""
+
+    def __init__(self, config, hidden_size: int, eps: float = 1e-5, out_dtype=None, weight_offset: float = 0.0):
+        super().__init__()
+        self.eps, self.hidden_size, self.out_dtype = eps, hidden_size, out_dtype
+        self.weight_offset = float(weight_offset)
+        dtype = config.params_dtype if config is not None else torch.float32
+        dev = "cpu" if (config is None or config.use_cpu_initialization or not torch.cuda.is_available()) \
+            else torch.cuda.current_device()
+        self.weight = nn.Parameter(torch.full((hidden_size,), 1.0 - self.weight_offset, dtype=dtype, device=dev))
+        setattr(self.weight, "sequence_parallel", bool(config.sequence_parallel) if config is not None else False)
+
+    def forward(self, x, out):
+        from ..ops import seqmix
+
+        shape, h = x.shape, x.shape[-1]
+        dt = self.out_dtype or self.weight.dtype
+        if isinstance(out, BranchPair):
+            x2, y = seqmix.norm_add(x.view(-1, h), out.a.reshape(-1, h), self.weight, self.eps, dt, self.weight_offset,
+                                    out.b.reshape(-1, h), out.weight_a, out.weight_b)
+        else:
+            x2, y = seqmix.norm_add(x.view(-1, h), out.reshape(-1, h), self.weight, self.eps, dt, self.weight_offset)
         return x2.view(shape), y.view(shape)
