@@ -1,5 +1,7 @@
 """Serving benchmark of the hybrid (Zikunex) design beside the closest existing model, a GPT decoder with grouped-query
-attention and the same feed-forwards, both through ``DynamicInferenceEngine.forward_tokens`` (``bench.py --serving``).
+attention and the same feed-forwards, both through ``DynamicInferenceEngine.forward_tokens`` (``bench.py --serving``);
+with ``--serving-design lerorax`` the Lerorax design beside its closest existing model, Zikunex, at equal width, depth and
+head sizes, and the Lerorax kernels beside their like kernels.
 
 Two parts, random weights, bf16:
 
@@ -93,6 +95,37 @@ def build_gpt(s, device):
     return model.to(device).eval()
 
 
+def lerorax_config(s):
+    """A Lerorax stack at the sizes of ``s``: side-by-side (head-mixing attention + delta memory) and minGRU layers in turn,
+    every fourth layer running the weights of the layer four below, clamped gated feed-forwards of the dense size's parameter
+    count."""
+    ff = {"kind": "dense", "ff": s["ff"] * 2 // 3 // 64 * 64, "limit": 7.0}
+    left = {"heads": s["heads"], "kv_heads": max(1, s["heads"] // 4), "dim": s["dim"], "vdim": s["dim"], "conv": 4,
+            "scale": s["dim"] ** -0.5, "rot": {"base": 500000.0, "dims": s["dim"] // 2,
+                                               "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": s["heads"], "dim": 64}
+    layers = []
+    for i in range(s["layers"]):
+        l = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": ff} if i % 2 == 0 else \
+            {"type": "mingru", "mixer": {"width": 2 * s["width"]}, "mlp": ff}
+        if i >= 4 and i % 4 in (2, 3):
+            l = dict(l, weights_of=i - 4)
+        layers.append(l)
+    return {"architecture": "Lerorax", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-5},
+            "embedding": {"bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 17}}, "layers": layers}
+
+
+def build_lerorax(s, device):
+    from .models.lerorax import LeroraxConfig, LeroraxModel
+    from .parallel import state as ps
+
+    if not ps.model_parallel_is_initialized():
+        ps.initialize_model_parallel(1, 1)
+    lcfg = LeroraxConfig.from_dict(lerorax_config(s))
+    base = lcfg.base_transformer_config(torch.bfloat16, use_cpu_initialization=False)
+    return LeroraxModel(lcfg, base).to(device).eval()
+
+
 def _engine(model, max_tokens, max_requests):
     from .data.tokenizer import NullTokenizer
     from .inference import DynamicInferenceEngine
@@ -142,6 +175,120 @@ def serve_numbers(model, vocab, prompts, prompt_len, decoders, context, steps, w
     for r in ids:
         ctx.release(r)
     return prompts * prompt_len / ms_prefill * 1e3, decoders / ms_decode * 1e3, ms_prefill, ms_decode
+
+
+def _kernel_bench(device):
+    """``(bench, out, roofline)``: ``bench(name, fn, bytes, flops, like)`` times ``fn`` alone (median of 5, an L2-sized buffer
+    rewritten before each) and records achieved rates and the fraction of the roofline in ``out``."""
+    hbm, how = _peaks()
+    fma_peak = 148 * 128 * 2 * 1.965e9 / 1e12        # fp32 TFLOP/s of the CUDA cores at the maximum clock
+    flush = torch.empty(160 << 20, dtype=torch.uint8, device=device)
+    out = {}
+
+    def bench(name, fn, nbytes, flops=0.0, like=None):
+        for _ in range(3):
+            fn()
+        ts = []
+        for _ in range(5):
+            flush.zero_()
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b))
+        ms = sorted(ts)[len(ts) // 2]
+        gbs = nbytes / ms / 1e6
+        tfl = flops / ms / 1e9
+        frac = max(gbs / hbm, tfl / fma_peak if flops else 0.0)
+        out[name] = {"ms": round(ms, 4), "GB/s": round(gbs, 1), "TFLOP/s": round(tfl, 2), "roofline_frac": round(frac, 3),
+                     "bound": "fma" if flops and tfl / fma_peak > gbs / hbm else "hbm", "like": like}
+
+    return bench, out, {"hbm_gbs": hbm, "fp32_fma_tflops": round(fma_peak, 1), "peaks": how}
+
+
+def kernel_numbers_lerorax(s, device):
+    """The kernels of the Lerorax mixers alone, each beside the like kernel of the closest model (Zikunex)."""
+    from . import ops
+    from .ops import seqmix
+
+    bench, out, roof = _kernel_bench(device)
+    H, d, W = s["heads"], s["dim"], s["width"]
+    G = max(1, H // 4)
+    bf = torch.bfloat16
+    rn = lambda *sh, **kw: torch.randn(*sh, device=device, **kw)  # noqa: E731
+    # -- decode attention: 64 requests x 2048 cached tokens; prefill: one prompt of 2048 tokens
+    R, L, bs = 64, 2048, 16
+    nblk = R * L // bs
+    table = torch.randperm(nblk, device=device).to(torch.int32).view(R, L // bs)
+    req = torch.arange(R, dtype=torch.int32, device=device)
+    lens = torch.full((R,), L, dtype=torch.int32, device=device)
+    kc, vc = rn(nblk * bs, G, d, dtype=bf), rn(nblk * bs, G, d, dtype=bf)
+    talk = rn(H, H) * 0.3
+    q = rn(R, H, d, dtype=bf)
+    gate = rn(R, H * d, dtype=bf)
+    bench("mixed_attention_paged.decode", lambda: seqmix.mixed_attention_paged(q, kc, vc, table, req, lens, bs, d ** -0.5, talk, gate, L),
+          R * L * G * d * 2 * 2, flops=R * L * H * d * 4, like="latent_attention_paged.decode")
+    r = s["kv_rank"]
+    cache = rn(nblk * bs, r, dtype=bf)
+    q_lat = rn(R, H, r, dtype=bf)
+    bench("latent_attention_paged.decode", lambda: seqmix.latent_attention_paged(q_lat, cache, table, req, lens, bs, 0.05, L),
+          R * L * r * 2, flops=R * L * H * r * 4)
+    T = 2048
+    table1 = torch.randperm(T // bs, device=device).to(torch.int32).view(1, -1)
+    req1 = torch.zeros(T, dtype=torch.int32, device=device)
+    len1 = torch.arange(1, T + 1, dtype=torch.int32, device=device)
+    q1, gate1 = rn(T, H, d, dtype=bf), rn(T, H * d, dtype=bf)
+    bench("mixed_attention_paged.prefill", lambda: seqmix.mixed_attention_paged(q1, kc, vc, table1, req1, len1, bs, d ** -0.5, talk, gate1, T),
+          T * G * d * 4 + T * H * d * 6, flops=T * (T + 1) / 2 * H * d * 4, like="latent_attention_paged.prefill")
+    q1l = rn(T, H, r, dtype=bf)
+    bench("latent_attention_paged.prefill", lambda: seqmix.latent_attention_paged(q1l, cache, table1, req1, len1, bs, 0.05, T),
+          T * r * 2 + T * H * r * 6, flops=T * (T + 1) / 2 * H * r * 4)
+    # -- matrix-memory scans: decode (64 sequences x 1 token, state bound) and prefill (4 x 2048 tokens, FMA bound); key dim 64
+    dd = 64
+    for tag, R_, n in (("decode", 64, 1), ("prefill", 4, 2048)):
+        T_ = R_ * n
+        pb = seqmix.PackedBatch([i * n for i in range(R_ + 1)], list(range(R_)), device)
+        rr, k, v = rn(T_, H, dd, dtype=bf), rn(T_, H, dd, dtype=bf), rn(T_, H, dd, dtype=bf)
+        wp, ap, wb = rn(T_, H * dd, dtype=bf), rn(T_, H * dd, dtype=bf), rn(H * dd, dtype=bf)
+        S = torch.zeros(R_, H, dd, dd, device=device)
+        state_bytes = R_ * H * dd * dd * 4 * 2
+        io = T_ * H * dd * 2 * 5 + T_ * H * dd * 4
+        bench(f"gen_delta_scan.{tag}", lambda: seqmix.gen_delta_scan(rr, k, v, wp, ap, wb, pb, S, 0.6), state_bytes + io,
+              flops=T_ * H * dd * dd * 10, like=f"delta_rule_scan.{tag}")
+        ld = -torch.rand(T_, H, dd, device=device) * 0.1
+        beta = torch.rand(T_, H, device=device)
+        bench(f"delta_rule_scan.{tag}", lambda: seqmix.delta_rule_scan(rr, k, v, ld, beta, pb, S),
+              state_bytes + T_ * H * dd * 2 * 3 + T_ * H * dd * 4 * 2, flops=T_ * H * dd * dd * 8)
+        C = 2 * W
+        zp, up, gp = rn(T_, C, dtype=bf), rn(T_, C, dtype=bf), rn(T_, C, dtype=bf)
+        Sg = torch.zeros(R_, C, device=device)
+        bench(f"mingru_scan.{tag}", lambda: seqmix.mingru_scan(zp, up, gp, pb, Sg), T_ * C * 2 * 4 + R_ * C * 8, like="add_rms_norm")
+    # -- norms, convolution, gate over 8192 tokens
+    T = 8192
+    x = rn(T, W)
+    a, b = rn(T, W, dtype=bf), rn(T, W, dtype=bf)
+    w = torch.ones(W, device=device, dtype=bf)
+    bench("norm_add", lambda: seqmix.norm_add(x, a, w, 1e-5, bf, 1.0), T * W * (4 + 4 + 2 + 2), like="add_rms_norm")
+    bench("norm_add (two branches)", lambda: seqmix.norm_add(x, a, w, 1e-5, bf, 1.0, b, w, w), T * W * (4 + 4 + 2 + 2 + 2), like="add_rms_norm")
+    bench("add_rms_norm", lambda: seqmix.add_rms_norm(x, a, w, 1e-5, bf), T * W * (4 + 4 + 2 + 2))
+    qk = rn(T, (H + 2 * G) * d, dtype=bf)
+    wq, wk = torch.ones(H * d, device=device, dtype=bf), torch.ones(G * d, device=device, dtype=bf)
+    pos = torch.arange(T, device=device)
+    inv = torch.rand(d // 4, device=device)
+    bench("norm_rope", lambda: seqmix.norm_rope(qk[:, :H * d], qk[:, H * d:(H + G) * d], wq, wk, pos, inv, d, d // 2, 1e-5),
+          T * (H + G) * d * 4, like="add_rms_norm")
+    C = (H + 2 * G) * d
+    wc = rn(C, 4, dtype=bf)
+    pbc = seqmix.PackedBatch([0, T], [0], device)
+    win = torch.zeros(1, 3, C, device=device, dtype=bf)
+    bench("causal_conv", lambda: seqmix.causal_conv(qk, wc, pbc, win), T * C * 4, like="causal_conv_silu")
+    bench("causal_conv_silu", lambda: seqmix.causal_conv_silu(qk, wc, pbc, win), T * C * 4)
+    F_ = s["ff"] * 2 // 3 // 64 * 64
+    xf = rn(T, 2 * F_, dtype=bf)
+    bench("clamped_glu", lambda: seqmix.clamped_glu(xf, 7.0), T * F_ * 6, like="swiglu")
+    bench("swiglu", lambda: ops.swiglu(xf, None), T * F_ * 6)
+    return out, roof
 
 
 def kernel_numbers(s, device):
@@ -266,8 +413,12 @@ def run(args):
            "warmup": max(3, args.warmup), "config": dict(s, prompts=4, prompt_len=2048, decoders=32, context=1024,
                                                         l2="model steps read weights and caches larger than L2; kernel "
                                                            "timings rewrite a 160 MB buffer between launches")}
+    design = getattr(args, "serving_design", "zikunex")
+    res["design"] = design
+    pairs = (("zikunex", build_zikunex), ("gpt_gqa_moe", build_gpt)) if design == "zikunex" else \
+        (("lerorax", build_lerorax), ("zikunex", build_zikunex))
     with torch.no_grad():
-        for name, build in (("zikunex", build_zikunex), ("gpt_gqa_moe", build_gpt)):
+        for name, build in pairs:
             t0 = time.time()
             model = build(s, dev)
             pre, dec, ms_p, ms_d = serve_numbers(model, s["vocab"], 4, 2048, 32, 1024, args.steps, max(3, args.warmup))
@@ -276,6 +427,7 @@ def run(args):
                          "build_s": round(time.time() - t0, 1)}
             del model
             torch.cuda.empty_cache()
-        res["kernels"], res["roofline"] = kernel_numbers(s, dev)
+        if not getattr(args, "serving_models_only", False):
+            res["kernels"], res["roofline"] = (kernel_numbers if design == "zikunex" else kernel_numbers_lerorax)(s, dev)
     print(json.dumps(res), flush=True)
     return res

@@ -227,7 +227,7 @@ void norm_rope(const Tensor& q, const Tensor& k, const Tensor& wq, const Tensor&
               wq.numel() == q.size(1) && wk.numel() == k.size(1), "bad norm weights");
   TORCH_CHECK(q_out.scalar_type() == q.scalar_type() && k_out.scalar_type() == q.scalar_type() && q_out.is_contiguous() &&
               k_out.is_contiguous() && q_out.numel() == q.numel() && k_out.numel() == k.numel(), "bad outputs");
-  TORCH_CHECK(std::max(q.size(1), k.size(1)) * sizeof(float) <= 48 * 1024, "projection too wide");
+  TORCH_CHECK((std::max(q.size(1), k.size(1)) + 1 + rot) * sizeof(float) <= 48 * 1024, "projection too wide");
   b200seq::NormRopeArgs p{};
   p.q = q.data_ptr(); p.k = k.data_ptr(); p.ldq = q.stride(0); p.ldk = k.stride(0);
   p.wq = wq.data_ptr(); p.wk = wk.data_ptr(); p.positions = positions.data_ptr<int64_t>(); p.inv_freq = inv_freq.data_ptr<float>();
@@ -241,7 +241,7 @@ void norm_rope(const Tensor& q, const Tensor& k, const Tensor& wq, const Tensor&
 
 void mixed_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor& vcache, const Tensor& block_table, const Tensor& tok_req,
                            const Tensor& tok_len, c10::optional<Tensor> talk, c10::optional<Tensor> gate, Tensor out, int64_t block_size,
-                           double scale, int64_t max_len) {
+                           double scale, int64_t max_len, bool force_generic) {
   const bool bf16 = act_is_bf16(q, "q");
   check_rows(q, "q");
   TORCH_CHECK(kcache.scalar_type() == q.scalar_type() && vcache.scalar_type() == q.scalar_type() && kcache.dim() == 3 && vcache.dim() == 3 &&
@@ -269,6 +269,8 @@ void mixed_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor& 
   p.block_size = static_cast<int>(block_size); p.max_blocks = static_cast<int>(block_table.size(1)); p.scale = static_cast<float>(scale);
   c10::cuda::CUDAGuard g(q.device());
   p.n_splits = b200seq::mixed_attention_splits(static_cast<int>(q.size(0)), static_cast<int>(max_len));
+  p.query_block = static_cast<int>(q.size(0) / std::max<int64_t>(1, block_table.size(0)));
+  p.force_generic = force_generic ? 1 : 0;
   Tensor ws1, ws2;
   if (p.n_splits > 1) {
     auto o32 = q.options().dtype(at::kFloat);
@@ -282,7 +284,8 @@ void mixed_attention_paged(const Tensor& q, const Tensor& kcache, const Tensor& 
 }
 
 void gen_delta_scan(const Tensor& r, const Tensor& k, const Tensor& v, const Tensor& w_pre, const Tensor& a_pre, c10::optional<Tensor> w_bias,
-                    const Tensor& cu, const Tensor& rows, Tensor state, Tensor out, double decay_scale, double unit_eps) {
+                    const Tensor& cu, const Tensor& rows, Tensor state, Tensor out, double decay_scale, double unit_eps,
+                    int64_t max_len) {
   const bool bf16 = act_is_bf16(r, "r");
   check_rows(r, "r"); check_rows(k, "k"); check_rows(v, "v");
   check_act2(w_pre, r, "w_pre"); check_act2(a_pre, r, "a_pre");
@@ -303,6 +306,7 @@ void gen_delta_scan(const Tensor& r, const Tensor& k, const Tensor& v, const Ten
   p.ldr = r.stride(0); p.ldk = k.stride(0); p.ldv = v.stride(0); p.ldw = w_pre.stride(0); p.lda = a_pre.stride(0);
   p.cu = cu.data_ptr<int>(); p.rows = rows.data_ptr<int>(); p.state = state.data_ptr<float>(); p.out = out.data_ptr<float>();
   p.decay_scale = static_cast<float>(decay_scale); p.unit_eps = static_cast<float>(unit_eps);
+  p.max_len = max_len > 0 ? static_cast<int>(max_len) : (1 << 30);
   c10::cuda::CUDAGuard g(r.device());
   TORCH_CHECK(b200seq::gen_delta_scan(p, static_cast<int>(rows.numel()), bf16, cur_stream()), "gen_delta_scan: key dim ", p.d,
               " above the largest kernel instance (256)");

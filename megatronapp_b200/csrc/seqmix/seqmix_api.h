@@ -78,6 +78,8 @@ struct MixAttnArgs {
   float* ws_stats;                // [T, n_splits, H, 2] when n_splits > 1
   float* ws_acc;                  // [T, n_splits, H * dv] when n_splits > 1
   int H, G, d, dv, block_size, max_blocks, n_splits;
+  int query_block;                // hint: new tokens per sequence in this step (>= 4: several queries share a key tile)
+  int force_generic;              // 1: the scalar kernel whatever the sizes (for tests)
   int key_tile, head_words, ldk_s;  // filled by the launcher
   float scale;
 };
@@ -91,6 +93,7 @@ struct GenDeltaArgs {
   float* state;                   // [rows, H, d, dv]
   float* out;                     // [T, H, dv]
   int H, d, dv;
+  int max_len;                    // the longest sequence of the step (0: unknown)
   float decay_scale, unit_eps;
 };
 

@@ -72,40 +72,101 @@ __global__ void __launch_bounds__(256) norm_add_kernel(float* __restrict__ x, co
 // q and k of a token: RMS norm over the whole projection (all heads at once) with a weight per channel, then rotation of the
 // first `rot` dimensions of every head, pairs (2i, 2i + 1), by angle position * inv_freq[i].  grid (tokens, 2): y = 0 is q.
 // ---------------------------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T> struct Pair;
+template <> struct Pair<float> {
+  static __device__ __forceinline__ float2 load(const float* p) { return *reinterpret_cast<const float2*>(p); }
+  static __device__ __forceinline__ void store(float* p, float2 v) { *reinterpret_cast<float2*>(p) = v; }
+};
+template <> struct Pair<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 load(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float2 v) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(v.x, v.y);
+  }
+};
+
+// PAIRED: even head width and strides, bases aligned for two-element accesses (the launcher checks); otherwise element by element.
+// The rot / 2 angles of a token are the same for all heads: cosine and sine are made once per CTA.
+template <typename T, bool PAIRED>
 __global__ void __launch_bounds__(256) norm_rope_kernel(NormRopeArgs p) {
-  extern __shared__ float row[];
+  extern __shared__ float row[];                                    // [n] values, then [rot] cosines and sines
   __shared__ float red[32];
   const int t = blockIdx.x, which = blockIdx.y;
   const int n = which == 0 ? p.q_ch : p.k_ch;
   const T* src = static_cast<const T*>(which == 0 ? p.q : p.k) + static_cast<int64_t>(t) * (which == 0 ? p.ldq : p.ldk);
   const T* w = static_cast<const T*>(which == 0 ? p.wq : p.wk);
   T* dst = static_cast<T*>(which == 0 ? p.q_out : p.k_out) + static_cast<int64_t>(t) * n;
+  float* cs = row + n + (n & 1);
+  const int half = p.rot / 2;
   float ss = 0.f;
-  for (int c = threadIdx.x; c < n; c += blockDim.x) {
-    const float v = ld(src + c);
-    row[c] = v;
-    ss += v * v;
+  constexpr int NP = 4;                                             // pairs a thread keeps in registers
+  const bool in_regs = PAIRED && n <= 2 * NP * 256;
+  float2 held[NP];
+  if (in_regs) {
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      const int c = 2 * (threadIdx.x + u * 256);
+      held[u] = c < n ? Pair<T>::load(src + c) : make_float2(0.f, 0.f);
+      ss += held[u].x * held[u].x + held[u].y * held[u].y;
+    }
+  } else if (PAIRED) {
+    for (int c = 2 * threadIdx.x; c < n; c += 2 * blockDim.x) {
+      const float2 v = Pair<T>::load(src + c);
+      row[c] = v.x; row[c + 1] = v.y;
+      ss += v.x * v.x + v.y * v.y;
+    }
+  } else {
+    for (int c = threadIdx.x; c < n; c += blockDim.x) {
+      const float v = ld(src + c);
+      row[c] = v;
+      ss += v * v;
+    }
   }
-  const float r = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(n) + p.eps);
-  for (int c = threadIdx.x; c < n; c += blockDim.x) row[c] = row[c] * r * ld(w + c);
-  __syncthreads();
-  const float pos = static_cast<float>(p.positions[t]);
-  const int half = p.rot / 2, pairs = p.head_dim / 2;               // head_dim and rot are even (checked on the host)
-  const int odd = p.head_dim & 1;
+  if (threadIdx.x < half) {
+    const float ang = static_cast<float>(p.positions[t]) * p.inv_freq[threadIdx.x];
+    cs[2 * threadIdx.x] = cosf(ang);
+    cs[2 * threadIdx.x + 1] = sinf(ang);
+  }
+  for (int i = threadIdx.x + blockDim.x; i < half; i += blockDim.x) {   // more than 256 rotated pairs per head
+    const float ang = static_cast<float>(p.positions[t]) * p.inv_freq[i];
+    cs[2 * i] = cosf(ang);
+    cs[2 * i + 1] = sinf(ang);
+  }
+  const float r = 1.0f / sqrtf(block_sum(ss, red) / static_cast<float>(n) + p.eps);   // its barriers also publish row and cs
+  const int pairs = p.head_dim / 2, odd = p.head_dim & 1;
+  if (in_regs) {
+#pragma unroll
+    for (int u = 0; u < NP; ++u) {
+      const int c = 2 * (threadIdx.x + u * 256);
+      if (c >= n) break;
+      const int i = (c % p.head_dim) >> 1;
+      const float2 wv = Pair<T>::load(w + c);
+      float a0 = held[u].x * r * wv.x, a1 = held[u].y * r * wv.y;
+      if (i < half) {
+        const float c_ = cs[2 * i], s_ = cs[2 * i + 1];
+        const float b0 = a0 * c_ - a1 * s_, b1 = a1 * c_ + a0 * s_;
+        a0 = b0; a1 = b1;
+      }
+      Pair<T>::store(dst + c, make_float2(a0, a1));
+    }
+    return;
+  }
   for (int e = threadIdx.x; e < (n / p.head_dim) * (pairs + odd); e += blockDim.x) {
     const int h = e / (pairs + odd), i = e % (pairs + odd);
     const int c = h * p.head_dim + 2 * i;
-    if (i >= pairs) { st(dst + c, row[c]); continue; }              // the last channel of an odd head width
-    float u = row[c], v = row[c + 1];
+    if (i >= pairs) { st(dst + c, row[c] * r * ld(w + c)); continue; }   // the last channel of an odd head width
+    float2 wv;
+    if (PAIRED) wv = Pair<T>::load(w + c);
+    else wv = make_float2(ld(w + c), ld(w + c + 1));
+    float u = row[c] * r * wv.x, v = row[c + 1] * r * wv.y;
     if (i < half) {
-      const float ang = pos * p.inv_freq[i];
-      const float cs = cosf(ang), sn = sinf(ang);
-      const float u2 = u * cs - v * sn, v2 = v * cs + u * sn;
+      const float c_ = cs[2 * i], s_ = cs[2 * i + 1];
+      const float u2 = u * c_ - v * s_, v2 = v * c_ + u * s_;
       u = u2; v = v2;
     }
-    st(dst + c, u);
-    st(dst + c + 1, v);
+    if (PAIRED) Pair<T>::store(dst + c, make_float2(u, v));
+    else { st(dst + c, u); st(dst + c + 1, v); }
   }
 }
 
@@ -271,6 +332,239 @@ __global__ void __launch_bounds__(kMixThreads) mixed_attention_kernel(MixAttnArg
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// The same attention for head sizes that 16-byte vectors divide (d and dv multiples of 8 for 16-bit, 4 for fp32 activations):
+// a CTA serves up to QB consecutive query tokens of one sequence with the same key tile (a block that straddles two sequences
+// walks them one after the other); key rows are copied and read 16 bytes at a time (rows padded to 128 m + 16 bytes, so a
+// quarter warp's rows fall into distinct banks); a thread owns one (query, key/value head, key) and keeps the key chunk in
+// registers for the heads of the group; values are not staged: in the weighted sum a thread owns 16 bytes of value channels of
+// one head and reads them from the cache once per key for all QB queries.  grid (token blocks, key splits), modes as above.
+// ---------------------------------------------------------------------------------------------------------------------
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int W = 4;
+  static __device__ __forceinline__ void load(const float* p, float* o) {
+    const float4 v = *reinterpret_cast<const float4*>(p);
+    o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w;
+  }
+  static __device__ __forceinline__ void store(float* p, const float* o) { *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]); }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int W = 8;
+  static __device__ __forceinline__ void load(const __nv_bfloat16* p, float* o) {
+    const uint4 v = *reinterpret_cast<const uint4*>(p);
+    o[0] = __uint_as_float(v.x << 16); o[1] = __uint_as_float(v.x & 0xffff0000u);
+    o[2] = __uint_as_float(v.y << 16); o[3] = __uint_as_float(v.y & 0xffff0000u);
+    o[4] = __uint_as_float(v.z << 16); o[5] = __uint_as_float(v.z & 0xffff0000u);
+    o[6] = __uint_as_float(v.w << 16); o[7] = __uint_as_float(v.w & 0xffff0000u);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, const float* o) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b = __floats2bfloat162_rn(o[2], o[3]);
+    __nv_bfloat162 c = __floats2bfloat162_rn(o[4], o[5]), d = __floats2bfloat162_rn(o[6], o[7]);
+    uint4 v;
+    v.x = *reinterpret_cast<unsigned*>(&a); v.y = *reinterpret_cast<unsigned*>(&b);
+    v.z = *reinterpret_cast<unsigned*>(&c); v.w = *reinterpret_cast<unsigned*>(&d);
+    *reinterpret_cast<uint4*>(p) = v;
+  }
+};
+
+constexpr int kHeadChunk = 4;
+
+template <typename T, int NI, int QB, int MODE>
+__global__ void __launch_bounds__(kMixThreads) mixed_attention_vec_kernel(MixAttnArgs p, int n_tok) {
+  constexpr int VW = Vec16<T>::W;
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  const int H = p.H, G = p.G, d = p.d, dv = p.dv, KT = p.key_tile, rep = H / G, ldk = p.ldk_s;
+  float* sq = reinterpret_cast<float*>(smem_raw);                  // [QB][H * d]
+  float* sS = sq + QB * H * d;                                     // [QB][H][KT]
+  float* sP = sS + QB * H * KT;                                    // [QB][H][KT]
+  float* sT = sP + QB * H * KT;                                    // [H * H]
+  float* sm = sT + H * H;                                          // [QB][H]
+  float* sl = sm + QB * H;                                         // [QB][H]
+  int* sslot = reinterpret_cast<int*>(sl + QB * H);                // [KT]
+  int* slen = sslot + KT;                                          // [QB]
+  T* sK = reinterpret_cast<T*>(smem_raw + static_cast<size_t>(p.head_words) * 4);
+  const int t_lo = blockIdx.x * QB, t_hi = min(n_tok, t_lo + QB), z = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kMixThreads >> 5;
+  const T* kc = static_cast<const T*>(p.kcache);
+  const T* vc = static_cast<const T*>(p.vcache);
+  const int n_out = H * dv / VW, dvc = dv / VW, krow = G * d / VW;
+  for (int e = threadIdx.x; e < H * H; e += kMixThreads) sT[e] = p.talk != nullptr ? p.talk[e] : ((e / H) == (e % H) ? 1.f : 0.f);
+  for (int seg_lo = t_lo; seg_lo < t_hi;) {
+    const int req = p.tok_req[seg_lo];
+    int seg_hi = seg_lo + 1;
+    while (seg_hi < t_hi && p.tok_req[seg_hi] == req) ++seg_hi;
+    const int nq = seg_hi - seg_lo;
+    const int* table = p.block_table + static_cast<int64_t>(req) * p.max_blocks;
+    __syncthreads();                                               // the previous segment is done with shared memory
+    for (int e = threadIdx.x; e < nq * H * d; e += kMixThreads)
+      sq[e] = ld(static_cast<const T*>(p.q) + static_cast<int64_t>(seg_lo + e / (H * d)) * p.ldq + e % (H * d)) * p.scale;
+    if (threadIdx.x < nq) slen[threadIdx.x] = p.tok_len[seg_lo + threadIdx.x];
+    if (MODE == 2) {
+      for (int e = warp; e < nq * H; e += n_warps) {               // merge the splits' statistics of (query, head) e
+        const float* ws = p.ws_stats + (static_cast<int64_t>(seg_lo + e / H) * p.n_splits * H + e % H) * 2;
+        float m = -INFINITY;
+        for (int s = lane; s < p.n_splits; s += 32) m = fmaxf(m, ws[static_cast<int64_t>(s) * H * 2]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int s = lane; s < p.n_splits; s += 32) {
+          const float ms = ws[static_cast<int64_t>(s) * H * 2];
+          if (ms != -INFINITY) l += ws[static_cast<int64_t>(s) * H * 2 + 1] * expf(ms - m);
+        }
+        l = warp_sum(l);
+        if (lane == 0) { sm[e] = m; sl[e] = l; }
+      }
+    } else {
+      for (int e = threadIdx.x; e < nq * H; e += kMixThreads) { sm[e] = -INFINITY; sl[e] = 0.f; }
+    }
+    const int max_len = p.tok_len[seg_hi - 1];                     // visible lengths grow along a sequence's tokens
+    const int per_split = (max_len + p.n_splits - 1) / p.n_splits;
+    const int key_lo = z * per_split, key_hi = min(max_len, key_lo + per_split);
+    float acc[NI][QB][VW];
+#pragma unroll
+    for (int n = 0; n < NI; ++n)
+#pragma unroll
+      for (int qi = 0; qi < QB; ++qi)
+#pragma unroll
+        for (int c = 0; c < VW; ++c) acc[n][qi][c] = 0.f;
+
+    for (int pass = (MODE == 2 ? 1 : 0); pass < (MODE == 1 ? 1 : 2); ++pass) {
+      for (int lo = key_lo; lo < key_hi; lo += KT) {
+        const int nk = min(KT, key_hi - lo);
+        __syncthreads();
+        for (int j = threadIdx.x; j < nk; j += kMixThreads) {
+          const int key = lo + j;
+          sslot[j] = table[key / p.block_size] * p.block_size + key % p.block_size;
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < nk * krow; e += kMixThreads) {
+          const int j = e / krow, c = e % krow;
+          *reinterpret_cast<uint4*>(sK + static_cast<size_t>(j) * ldk + c * VW) =
+              *reinterpret_cast<const uint4*>(kc + static_cast<int64_t>(sslot[j]) * G * d + c * VW);
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < nq * G * KT; e += kMixThreads) {   // scores: a thread per (query, key/value head, key)
+          const int j = e % KT, c = (e / KT) % G, qi = e / (KT * G);
+          const bool vis = j < nk && lo + j < slen[qi];
+          const T* kk = sK + static_cast<size_t>(j) * ldk + c * d;
+          for (int hc = 0; hc < rep; hc += kHeadChunk) {
+            float s[kHeadChunk];
+#pragma unroll
+            for (int r = 0; r < kHeadChunk; ++r) s[r] = 0.f;
+            if (vis) {
+              const float* qq = sq + (qi * H + c * rep + hc) * d;
+              for (int i = 0; i < d; i += VW) {
+                float kv[VW];
+                Vec16<T>::load(kk + i, kv);
+#pragma unroll
+                for (int r = 0; r < kHeadChunk; ++r) {
+                  if (hc + r < rep) {
+#pragma unroll
+                    for (int u = 0; u < VW; u += 4) {
+                      const float4 qv = *reinterpret_cast<const float4*>(qq + r * d + i + u);
+                      s[r] = fmaf(qv.x, kv[u], s[r]); s[r] = fmaf(qv.y, kv[u + 1], s[r]);
+                      s[r] = fmaf(qv.z, kv[u + 2], s[r]); s[r] = fmaf(qv.w, kv[u + 3], s[r]);
+                    }
+                  }
+                }
+              }
+            }
+#pragma unroll
+            for (int r = 0; r < kHeadChunk; ++r)
+              if (hc + r < rep) sS[(qi * H + c * rep + hc + r) * KT + j] = vis ? s[r] : -INFINITY;
+          }
+        }
+        __syncthreads();
+        if (pass == 0) {
+          for (int e = warp; e < nq * H; e += n_warps) {           // running maximum and sum of every (query, head)
+            float mx = -INFINITY;
+            for (int j = lane; j < nk; j += 32) mx = fmaxf(mx, sS[e * KT + j]);
+            mx = warp_max(mx);
+            if (mx == -INFINITY) continue;                         // nothing of this tile is visible to the query
+            const float m_old = sm[e], m_new = fmaxf(m_old, mx);
+            float sum = 0.f;
+            for (int j = lane; j < nk; j += 32) sum += expf(sS[e * KT + j] - m_new);
+            sum = warp_sum(sum);
+            if (lane == 0) {
+              sl[e] = (m_old == -INFINITY ? 0.f : sl[e] * expf(m_old - m_new)) + sum;
+              sm[e] = m_new;
+            }
+          }
+          continue;
+        }
+        for (int e = threadIdx.x; e < nq * H * KT; e += kMixThreads) {
+          const float sc = sS[e];
+          sS[e] = sc == -INFINITY ? 0.f : expf(sc - sm[e / KT]) / sl[e / KT];
+        }
+        __syncthreads();
+        for (int e = threadIdx.x; e < nq * H * KT; e += kMixThreads) {   // mixture across heads
+          const int j = e % KT, h = (e / KT) % H, qi = e / (KT * H);
+          const float* w = sS + qi * H * KT + j;
+          float m = 0.f;
+          for (int g = 0; g < H; ++g) m = fmaf(sT[h * H + g], w[g * KT], m);
+          sP[e] = m;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int n = 0; n < NI; ++n) {                             // weighted values: 16 bytes of one head's channels per thread
+          const int e = threadIdx.x + n * kMixThreads;
+          if (e < n_out) {
+            const int h = e / dvc, c = e % dvc;
+            const T* vv = vc + (h / rep) * dv + c * VW;
+            const float* pw = sP + h * KT;
+#pragma unroll 4
+            for (int j = 0; j < nk; ++j) {
+              float val[VW];
+              Vec16<T>::load(vv + static_cast<int64_t>(sslot[j]) * G * dv, val);
+#pragma unroll
+              for (int qi = 0; qi < QB; ++qi) {
+                const float w = pw[qi * H * KT + j];
+#pragma unroll
+                for (int u = 0; u < VW; ++u) acc[n][qi][u] = fmaf(w, val[u], acc[n][qi][u]);
+              }
+            }
+          }
+        }
+      }
+    }
+    if (MODE == 1) {
+      __syncthreads();
+      for (int e = threadIdx.x; e < nq * H; e += kMixThreads) {
+        float* ws = p.ws_stats + ((static_cast<int64_t>(seg_lo + e / H) * p.n_splits + z) * H + e % H) * 2;
+        ws[0] = sm[e]; ws[1] = sl[e];
+      }
+    } else {
+#pragma unroll
+      for (int n = 0; n < NI; ++n) {
+        const int e = threadIdx.x + n * kMixThreads;
+        if (e >= n_out) continue;
+#pragma unroll
+        for (int qi = 0; qi < QB; ++qi) {
+          if (qi >= nq) continue;
+          const int64_t t = seg_lo + qi;
+          if (MODE == 2) {
+            float* dst = p.ws_acc + (t * p.n_splits + z) * H * dv + e * VW;
+#pragma unroll
+            for (int u = 0; u < VW; ++u) dst[u] = acc[n][qi][u];
+          } else {
+            float o[VW];
+#pragma unroll
+            for (int u = 0; u < VW; ++u) o[u] = acc[n][qi][u];
+            if (p.gate != nullptr) {
+              float gv[VW];
+              Vec16<T>::load(static_cast<const T*>(p.gate) + t * p.ldg + e * VW, gv);
+#pragma unroll
+              for (int u = 0; u < VW; ++u) o[u] *= sigmoidf_(gv[u]);
+            }
+            Vec16<T>::store(static_cast<T*>(p.out) + t * H * dv + e * VW, o);
+          }
+        }
+      }
+    }
+    seg_lo = seg_hi;
+  }
+}
+
 template <typename T>
 __global__ void mixed_attention_merge_kernel(MixAttnArgs p, int n_tok) {
   const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
@@ -294,7 +588,7 @@ __global__ void mixed_attention_merge_kernel(MixAttnArgs p, int n_tok) {
 constexpr int kParts = 4;
 constexpr int kScanThreads = 128;
 constexpr int kColsPerCta = kScanThreads / kParts;
-template <int D> struct GenChunk { static constexpr int value = D > 128 ? 4 : (D > 64 ? 8 : 16); };
+template <int D> struct GenChunk { static constexpr int value = D > 128 ? 4 : (D > 64 ? 8 : 16); };   // tokens per shared-memory round
 
 __device__ __forceinline__ float part_sum(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);
@@ -302,10 +596,12 @@ __device__ __forceinline__ float part_sum(float v) {
   return v;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool LONG>
 __global__ void __launch_bounds__(kScanThreads) gen_delta_scan_kernel(GenDeltaArgs p) {
   constexpr int CH = GenChunk<D>::value, RP = D / kParts;
-  __shared__ float sr[CH][D], sk[CH][D], su[CH][D], sau[CH][D], sw[CH][D];
+  // per (token, key channel): x = unit key u, y = a * u, z = decay w, w = key k; the receptance r apart
+  __shared__ float4 sx[CH][D];
+  __shared__ float sr[CH][D];
   __shared__ float sv[CH][kColsPerCta];
   const int h = blockIdx.y, r = blockIdx.z;
   const int part = threadIdx.x & (kParts - 1);
@@ -327,54 +623,107 @@ __global__ void __launch_bounds__(kScanThreads) gen_delta_scan_kernel(GenDeltaAr
   const T* apre = static_cast<const T*>(p.a_pre);
   const T* wb = static_cast<const T*>(p.w_bias);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = kScanThreads >> 5;
+  // The next chunk's inputs are fetched into registers before the sequential part of the current one, so that their latency
+  // hides behind it; they move to shared memory (decay and removal rate made on the way) once the current chunk is done.
+  // (The widest instance has no registers to spare for that and fetches in place.)
+  constexpr bool PF = LONG && D <= 128;          // decoding keeps the registers for occupancy
+  constexpr int NS = PF ? CH * D / kScanThreads : 1, NV = PF ? (CH * kColsPerCta + kScanThreads - 1) / kScanThreads : 1;
+  float pr[NS], pk[NS], pw[NS], pa[NS], pv[NV];
+  auto prefetch = [&](int t0, int nt) {
+    if constexpr (!PF) return;
+#pragma unroll
+    for (int s = 0; s < NS; ++s) {
+      const int e = threadIdx.x + s * kScanThreads, tt = e / D, i = e % D;
+      const int64_t t = t0 + tt;
+      const bool in = tt < nt && i < p.d;
+      const int c = h * p.d + i;
+      pr[s] = in ? ld(rr + t * p.ldr + c) : 0.f;
+      pk[s] = in ? ld(k + t * p.ldk + c) : 0.f;
+      pw[s] = in ? ld(wpre + t * p.ldw + c) + (wb != nullptr ? ld(wb + c) : 0.f) : -INFINITY;   // sigmoid(-inf) = 0: decay 1
+      pa[s] = in ? ld(apre + t * p.lda + c) : -INFINITY;
+    }
+#pragma unroll
+    for (int s = 0; s < NV; ++s) {
+      const int e = threadIdx.x + s * kScanThreads, tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
+      pv[s] = (tt < nt && c < p.dv) ? ld(v + static_cast<int64_t>(t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
+    }
+  };
+  prefetch(a, min(CH, b - a));
   for (int t0 = a; t0 < b; t0 += CH) {
     const int nt = min(CH, b - t0);
     __syncthreads();                                  // the previous chunk has been consumed
-    for (int e = threadIdx.x; e < nt * D; e += kScanThreads) {
-      const int tt = e / D, i = e % D;
-      const int64_t t = t0 + tt;
-      const bool in = i < p.d;
-      const int c = h * p.d + i;
-      sr[tt][i] = in ? ld(rr + t * p.ldr + c) : 0.f;
-      sk[tt][i] = in ? ld(k + t * p.ldk + c) : 0.f;
-      sw[tt][i] = in ? expf(-p.decay_scale * sigmoidf_(ld(wpre + t * p.ldw + c) + (wb != nullptr ? ld(wb + c) : 0.f))) : 1.f;
-      sau[tt][i] = in ? sigmoidf_(ld(apre + t * p.lda + c)) : 0.f;
-    }
-    for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {
-      const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
-      sv[tt][e % kColsPerCta] = c < p.dv ? ld(v + static_cast<int64_t>(t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
+    if constexpr (PF) {
+#pragma unroll
+      for (int s = 0; s < NS; ++s) {
+        const int e = threadIdx.x + s * kScanThreads, tt = e / D, i = e % D;
+        if (tt < nt) {
+          sx[tt][i] = make_float4(0.f, sigmoidf_(pa[s]), expf(-p.decay_scale * sigmoidf_(pw[s])), pk[s]);
+          sr[tt][i] = pr[s];
+        }
+      }
+#pragma unroll
+      for (int s = 0; s < NV; ++s) {
+        const int e = threadIdx.x + s * kScanThreads;
+        if (e < nt * kColsPerCta) sv[e / kColsPerCta][e % kColsPerCta] = pv[s];
+      }
+    } else {
+      for (int e = threadIdx.x; e < nt * D; e += kScanThreads) {
+        const int tt = e / D, i = e % D, c = h * p.d + i;
+        const int64_t t = t0 + tt;
+        const bool in = i < p.d;
+        const float wz = in ? ld(wpre + t * p.ldw + c) + (wb != nullptr ? ld(wb + c) : 0.f) : -INFINITY;
+        sx[tt][i] = make_float4(0.f, in ? sigmoidf_(ld(apre + t * p.lda + c)) : 0.f, expf(-p.decay_scale * sigmoidf_(wz)),
+                                in ? ld(k + t * p.ldk + c) : 0.f);
+        sr[tt][i] = in ? ld(rr + t * p.ldr + c) : 0.f;
+      }
+      for (int e = threadIdx.x; e < nt * kColsPerCta; e += kScanThreads) {
+        const int tt = e / kColsPerCta, c = blockIdx.x * kColsPerCta + e % kColsPerCta;
+        sv[tt][e % kColsPerCta] = c < p.dv ? ld(v + static_cast<int64_t>(t0 + tt) * p.ldv + h * p.dv + c) : 0.f;
+      }
     }
     __syncthreads();
     for (int tt = warp; tt < nt; tt += n_warps) {     // unit keys and the removal direction a * u
       float kk = 0.f;
-      for (int i = lane; i < D; i += 32) kk += sk[tt][i] * sk[tt][i];
+      for (int i = lane; i < D; i += 32) kk += sx[tt][i].w * sx[tt][i].w;
       kk = warp_sum(kk);
       const float rk = 1.0f / sqrtf(kk + p.unit_eps);
       for (int i = lane; i < D; i += 32) {
-        const float u = sk[tt][i] * rk;
-        su[tt][i] = u;
-        sau[tt][i] *= u;
+        const float u = sx[tt][i].w * rk;
+        sx[tt][i].x = u;
+        sx[tt][i].y *= u;
       }
     }
     __syncthreads();
+    if (t0 + CH < b) prefetch(t0 + CH, min(CH, b - t0 - CH));
 #pragma unroll 1
     for (int tt = 0; tt < nt; ++tt) {
       const float vv = sv[tt][threadIdx.x >> 2];
+      constexpr bool KEEP = RP <= 16;                 // small key dims keep the token's operands in registers between the two loops
+      float4 x[KEEP ? RP : 1];
       float d0 = 0.f, d1 = 0.f;
 #pragma unroll
       for (int e = 0; e < RP; e += 2) {
-        d0 = fmaf(S[e], su[tt][e * kParts + part], d0);
-        d1 = fmaf(S[e + 1], su[tt][(e + 1) * kParts + part], d1);
+        if constexpr (KEEP) {
+          x[e] = sx[tt][e * kParts + part];
+          x[e + 1] = sx[tt][(e + 1) * kParts + part];
+          d0 = fmaf(S[e], x[e].x, d0);
+          d1 = fmaf(S[e + 1], x[e + 1].x, d1);
+        } else {
+          d0 = fmaf(S[e], sx[tt][e * kParts + part].x, d0);
+          d1 = fmaf(S[e + 1], sx[tt][(e + 1) * kParts + part].x, d1);
+        }
       }
       const float dot = part_sum(d0 + d1);
       float o0 = 0.f, o1 = 0.f;
 #pragma unroll
       for (int e = 0; e < RP; e += 2) {
-        const int i0 = e * kParts + part, i1 = (e + 1) * kParts + part;
-        S[e] = fmaf(sw[tt][i0], S[e], fmaf(-sau[tt][i0], dot, sk[tt][i0] * vv));
-        o0 = fmaf(S[e], sr[tt][i0], o0);
-        S[e + 1] = fmaf(sw[tt][i1], S[e + 1], fmaf(-sau[tt][i1], dot, sk[tt][i1] * vv));
-        o1 = fmaf(S[e + 1], sr[tt][i1], o1);
+        float4 xa, xb;
+        if constexpr (KEEP) { xa = x[e]; xb = x[e + 1]; }
+        else { xa = sx[tt][e * kParts + part]; xb = sx[tt][(e + 1) * kParts + part]; }
+        S[e] = fmaf(xa.z, S[e], fmaf(-xa.y, dot, xa.w * vv));
+        o0 = fmaf(S[e], sr[tt][e * kParts + part], o0);
+        S[e + 1] = fmaf(xb.z, S[e + 1], fmaf(-xb.y, dot, xb.w * vv));
+        o1 = fmaf(S[e + 1], sr[tt][(e + 1) * kParts + part], o1);
       }
       const float o = part_sum(o0 + o1);
       if (live && part == 0) p.out[(static_cast<int64_t>(t0 + tt) * p.H + h) * p.dv + col] = o;
@@ -398,6 +747,7 @@ __global__ void __launch_bounds__(kScanThreads) gen_delta_scan_kernel(GenDeltaAr
 // ---------------------------------------------------------------------------------------------------------------------
 constexpr int kGruRun = 64;
 constexpr int kGruThreads = 128;
+constexpr int kGruBatch = 8;
 
 __device__ __forceinline__ void gru_gates(float zp, float up, float* z, float* c) {
   *z = sigmoidf_(zp);
@@ -412,11 +762,23 @@ __global__ void __launch_bounds__(kGruThreads) mingru_reduce_kernel(MinGruArgs p
   const T* zp = static_cast<const T*>(p.z_pre);
   const T* up = static_cast<const T*>(p.u_pre);
   float P = 1.f, Q = 0.f;
-  for (int64_t t = a; t < b; ++t) {
-    float z, cand;
-    gru_gates(ld(zp + t * p.ldz + c), ld(up + t * p.ldu + c), &z, &cand);
-    P *= 1.f - z;
-    Q = fmaf(1.f - z, Q, z * cand);
+  for (int64_t t0 = a; t0 < b; t0 += kGruBatch) {     // the loads of a batch of tokens are issued before the dependent chain
+    float zv[kGruBatch], uv[kGruBatch];
+#pragma unroll
+    for (int j = 0; j < kGruBatch; ++j) {
+      const bool in = t0 + j < b;
+      zv[j] = in ? ld(zp + (t0 + j) * p.ldz + c) : 0.f;
+      uv[j] = in ? ld(up + (t0 + j) * p.ldu + c) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kGruBatch; ++j) {
+      if (t0 + j < b) {
+        float z, cand;
+        gru_gates(zv[j], uv[j], &z, &cand);
+        P *= 1.f - z;
+        Q = fmaf(1.f - z, Q, z * cand);
+      }
+    }
   }
   float* ws = p.ws + ((static_cast<int64_t>(r) * p.max_runs + blockIdx.y) * p.C + c) * 2;
   ws[0] = P; ws[1] = Q;
@@ -450,12 +812,24 @@ __global__ void __launch_bounds__(kGruThreads) mingru_apply_kernel(MinGruArgs p)
   T* y = static_cast<T*>(p.y);
   float* st_ = p.state + static_cast<int64_t>(p.rows[r]) * p.C + c;
   float S = CARRIED ? p.ws[((static_cast<int64_t>(r) * p.max_runs + blockIdx.y) * p.C + c) * 2] : *st_;
-  for (int64_t t = a; t < b; ++t) {
-    float z, cand;
-    gru_gates(ld(zp + t * p.ldz + c), ld(up + t * p.ldu + c), &z, &cand);
-    S = fmaf(1.f - z, S, z * cand);
-    const float g = ld(gp + t * p.ldg + c);
-    st(y + t * p.C + c, S * g * sigmoidf_(g));
+  for (int64_t t0 = a; t0 < b; t0 += kGruBatch) {
+    float zv[kGruBatch], uv[kGruBatch], gv[kGruBatch];
+#pragma unroll
+    for (int j = 0; j < kGruBatch; ++j) {
+      const bool in = t0 + j < b;
+      zv[j] = in ? ld(zp + (t0 + j) * p.ldz + c) : 0.f;
+      uv[j] = in ? ld(up + (t0 + j) * p.ldu + c) : 0.f;
+      gv[j] = in ? ld(gp + (t0 + j) * p.ldg + c) : 0.f;
+    }
+#pragma unroll
+    for (int j = 0; j < kGruBatch; ++j) {
+      if (t0 + j < b) {
+        float z, cand;
+        gru_gates(zv[j], uv[j], &z, &cand);
+        S = fmaf(1.f - z, S, z * cand);
+        st(y + (t0 + j) * p.C + c, S * gv[j] * sigmoidf_(gv[j]));
+      }
+    }
   }
   if (!CARRIED) *st_ = S;
 }
@@ -476,6 +850,26 @@ __global__ void clamped_glu_kernel(const T* __restrict__ x, int64_t ldx, T* __re
   st(y + idx, g * sigmoidf_(alpha * g) * (u + shift));
 }
 
+template <typename T>
+__global__ void clamped_glu_vec_kernel(const T* __restrict__ x, int64_t ldx, T* __restrict__ y, int64_t n_tok, int F, float limit,
+                                       float alpha, float shift) {
+  constexpr int VW = Vec16<T>::W;
+  const int per_row = F / VW;
+  const int64_t idx = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  if (idx >= n_tok * per_row) return;
+  const int64_t t = idx / per_row;
+  const int c = static_cast<int>(idx % per_row) * VW;
+  float g[VW], u[VW], o[VW];
+  Vec16<T>::load(x + t * ldx + c, g);
+  Vec16<T>::load(x + t * ldx + F + c, u);
+#pragma unroll
+  for (int i = 0; i < VW; ++i) {
+    const float gg = fminf(g[i], limit), uu = fminf(fmaxf(u[i], -limit), limit);
+    o[i] = gg * sigmoidf_(alpha * gg) * (uu + shift);
+  }
+  Vec16<T>::store(y + t * F + c, o);
+}
+
 }  // namespace
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -491,8 +885,15 @@ void norm_add(float* x, const void* a, const void* b, const void* wa, const void
 
 void norm_rope(const NormRopeArgs& p, int n_tok, bool bf16, cudaStream_t s) {
   if (n_tok == 0) return;
-  const size_t smem = static_cast<size_t>(std::max(p.q_ch, p.k_ch)) * sizeof(float);
-  SEQ_DISPATCH_T(bf16, norm_rope_kernel<T><<<dim3(n_tok, 2), 256, smem, s>>>(p));
+  const size_t smem = static_cast<size_t>(std::max(p.q_ch, p.k_ch) + 1 + p.rot) * sizeof(float);
+  const size_t two = bf16 ? 4 : 8;
+  auto al = [&](const void* q) { return reinterpret_cast<uintptr_t>(q) % two == 0; };
+  const bool paired = p.head_dim % 2 == 0 && p.ldq % 2 == 0 && p.ldk % 2 == 0 && al(p.q) && al(p.k) && al(p.wq) && al(p.wk) &&
+                      al(p.q_out) && al(p.k_out);
+  SEQ_DISPATCH_T(bf16, {
+    if (paired) norm_rope_kernel<T, true><<<dim3(n_tok, 2), 256, smem, s>>>(p);
+    else norm_rope_kernel<T, false><<<dim3(n_tok, 2), 256, smem, s>>>(p);
+  });
 }
 
 int mixed_attention_splits(int n_tok, int max_len) {
@@ -542,8 +943,72 @@ static bool launch_mix(MixAttnArgs p, int n_tok, cudaStream_t s) {
   return true;
 }
 
+// the vector kernel's shared-memory plan for a query block of qb tokens and a tile of kt keys
+static size_t vec_smem(const MixAttnArgs& p, int qb, int kt, size_t elt, int* head_words, int* ldk) {
+  int words = qb * p.H * p.d + 2 * qb * p.H * kt + p.H * p.H + 2 * qb * p.H + kt + qb;
+  words = (words + 3) / 4 * 4;
+  const size_t row_bytes = (static_cast<size_t>(p.G) * p.d * elt + 127) / 128 * 128 + 16;
+  *head_words = words; *ldk = static_cast<int>(row_bytes / elt);
+  return static_cast<size_t>(words) * 4 + static_cast<size_t>(kt) * row_bytes;
+}
+
+template <typename T, int NI, int QB>
+static bool launch_vec(MixAttnArgs p, int n_tok, int kt, cudaStream_t s) {
+  const size_t smem = vec_smem(p, QB, kt, sizeof(T), &p.head_words, &p.ldk_s);
+  p.key_tile = kt;
+  auto set = [&](auto kern) {
+    return smem <= 48 * 1024 || cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem)) == cudaSuccess;
+  };
+  const int blocks = (n_tok + QB - 1) / QB;
+  if (p.n_splits == 1) {
+    auto kern = mixed_attention_vec_kernel<T, NI, QB, 0>;
+    if (!set(kern)) return false;
+    kern<<<dim3(blocks, 1), kMixThreads, smem, s>>>(p, n_tok);
+    return true;
+  }
+  auto k1 = mixed_attention_vec_kernel<T, NI, QB, 1>;
+  auto k2 = mixed_attention_vec_kernel<T, NI, QB, 2>;
+  if (!set(k1) || !set(k2)) return false;
+  k1<<<dim3(blocks, p.n_splits), kMixThreads, smem, s>>>(p, n_tok);
+  k2<<<dim3(blocks, p.n_splits), kMixThreads, smem, s>>>(p, n_tok);
+  const int64_t n = static_cast<int64_t>(n_tok) * p.H * p.dv;
+  mixed_attention_merge_kernel<T><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(p, n_tok);
+  return true;
+}
+
+// 0: sizes or alignment the vector kernel does not take; 1: launched; -1: launch failed
+template <typename T>
+static int try_vec(const MixAttnArgs& p, int n_tok, cudaStream_t s) {
+  constexpr int VW = Vec16<T>::W;
+  auto al = [](const void* q) { return reinterpret_cast<uintptr_t>(q) % 16 == 0; };
+  if (p.d % VW || p.dv % VW || p.ldq % VW || !al(p.q) || !al(p.kcache) || !al(p.vcache) || !al(p.out) ||
+      (p.gate != nullptr && (!al(p.gate) || p.ldg % VW)))
+    return 0;
+  const int ni = (p.H * p.dv / VW + kMixThreads - 1) / kMixThreads;
+  if (ni > 4) return 0;
+  // several queries per CTA once the step brings many tokens per sequence and the grid still fills the GPU
+  int qb = (p.query_block >= 4 && p.n_splits == 1 && ni <= 2) ? 4 : 1;
+  int hw, ldk, kt = 0;
+  for (;; qb = 1) {
+    for (kt = 64; kt >= 16; kt /= 2)
+      if (vec_smem(p, qb, kt, sizeof(T), &hw, &ldk) <= 96 * 1024) break;
+    if (kt >= 16 || qb == 1) break;
+  }
+  if (kt < 16) return 0;
+  bool ok = false;
+  if (qb == 4) ok = ni == 1 ? launch_vec<T, 1, 4>(p, n_tok, kt, s) : launch_vec<T, 2, 4>(p, n_tok, kt, s);
+  else if (ni == 1) ok = launch_vec<T, 1, 1>(p, n_tok, kt, s);
+  else if (ni == 2) ok = launch_vec<T, 2, 1>(p, n_tok, kt, s);
+  else ok = launch_vec<T, 4, 1>(p, n_tok, kt, s);
+  return ok ? 1 : -1;
+}
+
 template <typename T>
 static bool dispatch_mix(const MixAttnArgs& p, int n_tok, cudaStream_t s) {
+  if (!p.force_generic) {
+    const int v = try_vec<T>(p, n_tok, s);
+    if (v != 0) return v > 0;
+  }
   const int per = (p.H * p.dv + kMixThreads - 1) / kMixThreads;
   if (per <= 1) return launch_mix<T, 1>(p, n_tok, s);
   if (per <= 2) return launch_mix<T, 2>(p, n_tok, s);
@@ -562,11 +1027,15 @@ bool mixed_attention_paged(const MixAttnArgs& p, int n_tok, bool bf16, cudaStrea
 
 template <typename T>
 static bool launch_gen_delta(const GenDeltaArgs& p, dim3 grid, cudaStream_t s) {
-  if (p.d <= 32) gen_delta_scan_kernel<T, 32><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 64) gen_delta_scan_kernel<T, 64><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 128) gen_delta_scan_kernel<T, 128><<<grid, kScanThreads, 0, s>>>(p);
-  else if (p.d <= 256) gen_delta_scan_kernel<T, 256><<<grid, kScanThreads, 0, s>>>(p);
+#define SEQ_GEN_DELTA(DD)                                                                                       \
+  if (p.max_len > GenChunk<DD>::value) gen_delta_scan_kernel<T, DD, true><<<grid, kScanThreads, 0, s>>>(p);     \
+  else gen_delta_scan_kernel<T, DD, false><<<grid, kScanThreads, 0, s>>>(p)
+  if (p.d <= 32) { SEQ_GEN_DELTA(32); }
+  else if (p.d <= 64) { SEQ_GEN_DELTA(64); }
+  else if (p.d <= 128) { SEQ_GEN_DELTA(128); }
+  else if (p.d <= 256) { SEQ_GEN_DELTA(256); }
   else return false;
+#undef SEQ_GEN_DELTA
   return true;
 }
 
@@ -594,6 +1063,13 @@ void clamped_glu(const void* x, int64_t ldx, void* y, int64_t n_tok, int F, floa
                  cudaStream_t s) {
   const int64_t n = n_tok * F;
   if (n == 0) return;
+  const int vw = bf16 ? 8 : 4;
+  if (F % vw == 0 && ldx % vw == 0 && reinterpret_cast<uintptr_t>(x) % 16 == 0 && reinterpret_cast<uintptr_t>(y) % 16 == 0) {
+    const int64_t nv = n / vw;
+    SEQ_DISPATCH_T(bf16, clamped_glu_vec_kernel<T><<<static_cast<unsigned>((nv + 255) / 256), 256, 0, s>>>(
+                             static_cast<const T*>(x), ldx, static_cast<T*>(y), n_tok, F, limit, alpha, shift));
+    return;
+  }
   SEQ_DISPATCH_T(bf16, clamped_glu_kernel<T><<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(
                            static_cast<const T*>(x), ldx, static_cast<T*>(y), n_tok, F, limit, alpha, shift));
 }

@@ -375,12 +375,15 @@ def norm_rope(q: torch.Tensor, k: torch.Tensor, weight_q: torch.Tensor, weight_k
 
 def mixed_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, block_table: torch.Tensor,
                           tok_req: torch.Tensor, tok_len: torch.Tensor, block_size: int, scale: float,
-                          talk: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, max_len: int = 0) -> torch.Tensor:
+                          talk: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None, max_len: int = 0,
+                          force_generic: bool = False) -> torch.Tensor:
     """``q [T, H, d]`` against paged keys ``[slots, G, d]`` and values ``[slots, G, dv]``: per head the ordinary softmax
     over the ``tok_len[t]`` visible keys of the token's sequence; the weights of all heads are then mixed,
     ``M_h = sum_g talk[h, g] P_g`` (``talk`` fp32 ``[H, H]``; ``None``: no mixing), and head ``h`` applies ``M_h`` to the
     values of its own key/value head ``h // (H / G)``.  ``gate [T, H * dv]`` (pre-activation) multiplies the result by
-    its sigmoid.  Scores, weights and sums are fp32.  Returns ``[T, H * dv]`` in ``q``'s dtype."""
+    its sigmoid.  Scores, weights and sums are fp32.  Returns ``[T, H * dv]`` in ``q``'s dtype.  Head sizes that 16-byte
+    vectors divide take the vector kernel (several queries of a prompt per CTA), others the scalar one (``force_generic``
+    selects it regardless, for tests)."""
     T, H, d = q.shape
     G, dv = kcache.shape[1], vcache.shape[2]
     if q.is_cuda:
@@ -389,7 +392,7 @@ def mixed_attention_paged(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.T
         ext().mixed_attention_paged(_rows3(q), kcache, vcache, block_table, tok_req, tok_len,
                                     None if talk is None else talk.float().contiguous(),
                                     None if gate is None else (gate if gate.stride(1) == 1 else gate.contiguous()), o,
-                                    int(block_size), float(scale), int(max_len))
+                                    int(block_size), float(scale), int(max_len), bool(force_generic))
         return o
     o = torch.empty(T, H, dv, dtype=torch.float32)
     req, lens = tok_req.tolist(), tok_len.tolist()
@@ -437,7 +440,7 @@ def gen_delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w_pre: tor
         o = torch.empty(T, H, dv, dtype=torch.float32, device=r.device)
         ext().gen_delta_scan(_rows3(r), _rows3(k), _rows3(v), w_pre if w_pre.stride(1) == 1 else w_pre.contiguous(),
                              a_pre if a_pre.stride(1) == 1 else a_pre.contiguous(), w_bias, pb.cu, pb.slots, state, o,
-                             float(decay_scale), float(unit_eps))
+                             float(decay_scale), float(unit_eps), pb.max_len)
         return o
     rf, kf, vf = r.float(), k.float(), v.float()
     wz = w_pre.float() + (w_bias.float() if w_bias is not None else 0.0)

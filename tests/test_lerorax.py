@@ -293,11 +293,12 @@ def test_bfloat16_kernels_stay_within_rounding():
 # hand-made inputs: what random weights would hide
 # ---------------------------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("dv", [6, 8], ids=["scalar_kernel", "vector_kernel"])
 @pytest.mark.parametrize("ctx_len,far", [(5, 0), (64, 0), (65, 1), (300, 3), (300, 4), (1200, 7), (1200, 1199)])
-def test_attention_finds_one_far_key_across_pages(ctx_len, far, device):
+def test_attention_finds_one_far_key_across_pages(ctx_len, far, dv, device):
     """One key among hundreds matches the last query; its value must come through whatever page or tile edge it sits at, and
     only through the heads that the mixing matrix routes it to."""
-    H, G, d, dv, bs = 4, 2, 8, 6, 4
+    H, G, d, bs = 4, 2, 8, 4
     g = torch.Generator().manual_seed(ctx_len + far)
     k = torch.randn(ctx_len, G, d, generator=g) * 0.1
     v = torch.randn(ctx_len, G, dv, generator=g)
@@ -399,6 +400,43 @@ def test_config_rejects_bad_layer_references():
         LeroraxConfig.from_dict(config_of([layer(GRU, weights_of=1), layer(GRU, weights_of=0)]))   # nobody owns tensors
     lcfg = LeroraxConfig.from_dict(HYBRID)
     assert lcfg.owners() == [0, 1, 2, 4, 6] and lcfg.owner(7) == 0
+
+
+@pytest.mark.parametrize("device", DEVICES)
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16], ids=["fp32", "bf16"])
+def test_attention_prompt_portions_of_several_sequences_in_one_batch(dtype, device):
+    """Three sequences with 0, 9 and 130 cached tokens bring 70, 1 and 3 new ones: query blocks of the vector kernel straddle
+    the sequences, and every query sees exactly its own prefix.  Both kernels against the oracle's attention."""
+    H, G, d, dv, bs = 4, 2, 16, 8, 4
+    g = torch.Generator().manual_seed(11)
+    before, new = [0, 9, 130], [70, 1, 3]
+    talk = torch.eye(H) * 0.6 + torch.randn(H, H, generator=g) * 0.3
+    nb = [-(-(b + n) // bs) for b, n in zip(before, new)]
+    perm = torch.randperm(sum(nb), generator=g)
+    table = torch.zeros(3, max(nb), dtype=torch.int32)
+    kc, vc = torch.zeros(sum(nb) * bs, G, d), torch.zeros(sum(nb) * bs, G, dv)
+    qs, req, lens, want, at = [], [], [], [], 0
+    for r, (b, n) in enumerate(zip(before, new)):
+        table[r, :nb[r]] = perm[at:at + nb[r]].to(torch.int32)
+        at += nb[r]
+        L = b + n
+        q, k, v = (torch.randn(L, H, d, generator=g), torch.randn(L, G, d, generator=g), torch.randn(L, G, dv, generator=g))
+        q, k, v = (t.to(dtype).float() for t in (q, k, v))
+        pos = torch.arange(L)
+        slots = table[r].long()[pos // bs] * bs + pos % bs
+        kc[slots], vc[slots] = k, v
+        want.append(oracle.head_mixing_attention(q.double(), k.double(), v.double(), 0.25, talk.double())[b:])
+        qs.append(q[b:])
+        req += [r] * n
+        lens += list(range(b + 1, L + 1))
+    gate = torch.randn(sum(new), H * dv, generator=g).to(dtype)
+    ref = torch.cat(want).reshape(-1, H * dv) * torch.sigmoid(gate.double())
+    to = lambda t: t.to(device)  # noqa: E731
+    for generic in (False, True):
+        o = seqmix.mixed_attention_paged(to(torch.cat(qs).to(dtype)), to(kc.to(dtype)), to(vc.to(dtype)), to(table),
+                                         to(torch.tensor(req, dtype=torch.int32)), to(torch.tensor(lens, dtype=torch.int32)), bs, 0.25,
+                                         to(talk), to(gate), 133, force_generic=generic)
+        close(o, ref, 1e-4 if dtype == torch.float32 else 2e-2)
 
 
 # ---------------------------------------------------------------------------------------------------------------------
