@@ -456,7 +456,7 @@ def write_model_folder(path, cfg, W):
         f.write(struct.pack("<Q", len(h)) + h + b"".join(blobs))
 
 
-def test_model_folder_through_registry_and_trace_runner(tmp_path):
+def test_model_folder_through_registry_trace_runner_and_cli(tmp_path):
     import numpy as np
 
     root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -481,3 +481,14 @@ def test_model_folder_through_registry_and_trace_runner(tmp_path):
     close(got[1], wb[4:5], TOL[torch.float32])
     close(got[2], torch.stack([wa[17], wb[5]]), TOL[torch.float32])
     close(got[3], wa[18:19], TOL[torch.float32])
+    # the generation command line on the same folder: greedy tokens of the oracle
+    import sys
+
+    r = subprocess.run([sys.executable, os.path.join(root, "tools", "run_text_generation_server.py"), "--model-dir", str(tmp_path),
+                        "--dtype", "float32", "--prompts", " ".join(map(str, b)), "--num-tokens-to-generate", "4"],
+                       capture_output=True, text=True, env=env, timeout=600)
+    assert r.returncode == 0, r.stderr[-2000:]
+    toks = list(b)
+    for _ in range(4):
+        toks.append(int(oracle.forward(cfg, W, toks)[-1].argmax()))
+    assert r.stdout.strip().splitlines()[-1].endswith("-> " + repr(" ".join(map(str, toks[len(b):]))))
