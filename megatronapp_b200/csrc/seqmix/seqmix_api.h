@@ -58,7 +58,7 @@ bool group_limited_router(const float* logits, float* probs, bool* rmap, int n_t
 struct NormRopeArgs {
   const void *q, *k;              // [T, q_ch], [T, k_ch] with row strides ldq / ldk (elements)
   int64_t ldq, ldk;
-  const void *wq, *wk;            // norm weights over the whole projection
+  const void *wq, *wk;            // norm weights, one per channel of all heads
   const int64_t* positions;       // [T]
   const float* inv_freq;          // [rot / 2]
   void *q_out, *k_out;            // contiguous [T, q_ch], [T, k_ch]

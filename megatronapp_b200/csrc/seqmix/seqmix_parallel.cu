@@ -69,7 +69,7 @@ __global__ void __launch_bounds__(256) norm_add_kernel(float* __restrict__ x, co
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
-// q and k of a token: RMS norm over the whole projection (all heads at once) with a weight per channel, then rotation of the
+// q and k of a token: one RMS norm across all heads' channels, with a weight per channel, then rotation of the
 // first `rot` dimensions of every head, pairs (2i, 2i + 1), by angle position * inv_freq[i].  grid (tokens, 2): y = 0 is q.
 // ---------------------------------------------------------------------------------------------------------------------
 template <typename T> struct Pair;
@@ -580,7 +580,7 @@ __global__ void mixed_attention_merge_kernel(MixAttnArgs p, int n_tok) {
 
 // ---------------------------------------------------------------------------------------------------------------------
 // Generalized delta rule.  Per head, per token, with the unit key u = k / sqrt(sum k^2 + unit_eps):
-//   S <- diag(w) S - (a * u) (u^T S) + k v^T   (both terms read the old S);   o = S^T r
+//   S <- diag(w) S - (a * u) (u^T S) + k v^T   (decay and removal both act on the previous S);   o = S^T r
 //   w = exp(-decay_scale * sigmoid(w_pre + w_bias)),  a = sigmoid(a_pre)
 // Layout as the gated delta-rule scan of seqmix.cu: grid (column blocks, heads, sequences), a column of S shared by kParts
 // lanes, a chunk of tokens staged in shared memory (decays, removal rates and unit keys are made there, in fp32).
@@ -588,7 +588,7 @@ __global__ void mixed_attention_merge_kernel(MixAttnArgs p, int n_tok) {
 constexpr int kParts = 4;
 constexpr int kScanThreads = 128;
 constexpr int kColsPerCta = kScanThreads / kParts;
-template <int D> struct GenChunk { static constexpr int value = D > 128 ? 4 : (D > 64 ? 8 : 16); };   // tokens per shared-memory round
+template <int D> struct GenChunk { static constexpr int value = D > 128 ? 4 : (D > 64 ? 8 : 16); };   // tokens staged in shared memory at a time
 
 __device__ __forceinline__ float part_sum(float v) {
   v += __shfl_xor_sync(0xffffffffu, v, 1);

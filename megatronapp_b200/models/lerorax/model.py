@@ -1,5 +1,5 @@
 """Lerorax: a decoder-only hybrid.  Word embedding plus a hashed bigram embedding; layers that norm their sublayers'
-*outputs* (``x <- x + norm(mixer(x))``, ``x <- x + norm(mlp(x))``, weights stored around zero) over an fp32 residual
+*outputs* (``x <- x + norm(mixer(x))``, ``x <- x + norm(mlp(x))``, zero-centred norm weights, applied as 1 + w) over an fp32 residual
 stream; two kinds of mixer -- attention with head mixing side by side with a generalized delta-rule memory, or a minGRU --
 and a clamped gated feed-forward.  A layer may run another layer's weights with a cache of its own.
 
@@ -24,7 +24,7 @@ from ..common.language_module import LanguageModule
 from .config import DEFAULT_DECAY_RANK, LeroraxConfig
 
 _MLP_SUB = MLPSubmodules(linear_fc1=ColumnParallelLinear, linear_fc2=RowParallelLinear)
-NORM_WEIGHT_OFFSET = 1.0          # layer and final norm weights are stored around zero
+NORM_WEIGHT_OFFSET = 1.0          # layer and final norm weights are zero-centred: applied as 1 + w
 
 
 def build_mixer(lcfg: LeroraxConfig, base, index: int):

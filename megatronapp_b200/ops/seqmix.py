@@ -98,8 +98,8 @@ class PackedBatch:
 def add_rms_norm(x: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor, eps: float,
                  out_dtype: torch.dtype, weight_offset: float = 0.0) -> Tuple[torch.Tensor, torch.Tensor]:
     """``x`` fp32 ``[T, h]`` (updated in place by ``+ delta`` when given) -> ``(x, rms_norm(x) * (weight_offset + weight))``;
-    the normalised copy leaves in ``out_dtype``, the statistics are fp32.  ``weight_offset = 1`` is a weight stored around
-    zero."""
+    the normalised copy leaves in ``out_dtype``, the statistics are fp32.  ``weight_offset = 1`` serves a zero-centred
+    weight."""
     if x.is_cuda:
         kernel_calls["add_rms_norm"] += 1
         y = torch.empty(x.shape, dtype=out_dtype, device=x.device)
@@ -431,7 +431,7 @@ def gen_delta_scan(r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, w_pre: tor
     -> ``o [T, H, dv]`` fp32.  Per head and token, with ``u = k / sqrt(sum k^2 + unit_eps)``::
 
         w = exp(-decay_scale * sigmoid(w_pre + w_bias));  a = sigmoid(a_pre)
-        S <- diag(w) S - (a * u) (u^T S) + k v^T   (both terms read the old S);   o = S^T r
+        S <- diag(w) S - (a * u) (u^T S) + k v^T   (decay and removal both act on the previous S);   o = S^T r
     """
     T, H, dv = v.shape
     d = r.shape[2]

@@ -4,7 +4,7 @@ Per head a memory ``S [d, dv]`` is carried from token to token; with the unit ke
 
     w = exp(-decay_scale * sigmoid(W_w2 tanh(W_w1 h) + w_0))        decay per key channel, in (exp(-decay_scale), 1)
     a = sigmoid(W_a h + b_a)                                         removal rate per key channel
-    S <- diag(w) S - (a * u) (u^T S) + k v^T                         both terms read the old S
+    S <- diag(w) S - (a * u) (u^T S) + k v^T                         decay and removal both act on the previous S
     o = S^T r
 
 The read-out is RMS-normalised head by head, scaled by one weight vector over all heads' channels, gated by

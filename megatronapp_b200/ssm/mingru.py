@@ -1,4 +1,4 @@
-"""minGRU mixer: a gated recurrence per channel whose gates read only the current token, so that it is a linear scan.
+"""minGRU mixer: a per-channel gated recurrence whose gates do not depend on the previous state, which makes it a linear scan.
 
     z = sigmoid(W_z h + b_z);  u = W_x h + b_x;  c = u + 1/2 where u >= 0, sigmoid(u) elsewhere
     S <- (1 - z) S + z c;  y = W_o (S * silu(W_g h))

@@ -1,5 +1,5 @@
-"""Grouped-query softmax attention whose weights are mixed across heads, with a short convolution on q / k / v, a norm
-over the whole q and k projections, partial interleaved rotary positions and a sigmoid output gate.
+"""Grouped-query softmax attention whose weights are mixed across heads, with a short convolution on q / k / v, one RMS norm
+across all heads' channels of q (and one of k), partial interleaved rotary positions and a sigmoid output gate.
 
 Per token, from the mixer input ``h``::
 

@@ -76,7 +76,7 @@ class ResidualRMSNorm(nn.Module):
     def __init__(self, config, hidden_size: int, eps: float = 1e-5, out_dtype=None, weight_offset: float = 0.0):
         super().__init__()
         self.eps, self.hidden_size = eps, hidden_size
-        self.weight_offset = float(weight_offset)     # 1.0: the weight is stored around zero and applied as 1 + w
+        self.weight_offset = float(weight_offset)     # 1.0: zero-centred weight, applied as 1 + w
         dtype = config.params_dtype if config is not None else torch.float32
         self.out_dtype = out_dtype          # None: the weight's dtype at call time
         dev = "cpu" if (config is None or config.use_cpu_initialization or not torch.cuda.is_available()) \
