@@ -235,6 +235,26 @@ def test_unequal_batch_matches_each_alone_and_rows_are_reused(device):
 
 
 @pytest.mark.parametrize("device", DEVICES)
+def test_other_sizes_five_taps_no_rotation_many_heads_per_group(device):
+    """Sizes none of the other tests use: five convolution taps (the generic convolution kernel and a four-row window), no
+    rotated dimensions at all, eight query heads per key/value head, a value width that is a multiple of the key width, an
+    odd minGRU width first in the stack, a model without bigram table and a feed-forward limit that never binds."""
+    left = {"heads": 16, "kv_heads": 2, "dim": 8, "vdim": 48, "conv": 5, "scale": 0.3, "rot": {"base": 100.0, "dims": 0}}
+    left2 = {"heads": 5, "dim": 24, "conv": 1, "scale": 0.11, "rot": {"base": 777.0, "dims": 24,
+                                                                       "scaling": {"factor": 2.0, "low": 2.0, "high": 4.0, "original": 16}}}
+    cfg = config_of([layer(GRU_B, {"kind": "dense", "ff": 24, "limit": 50.0}),
+                     layer({"type": "parallel", "mixer": {"left": left, "right": {"heads": 5, "dim": 16}}}, FF),
+                     layer({"type": "parallel", "mixer": {"left": left2, "right": {"heads": 1, "dim": 96}}})],
+                    width=136, vocab=300, eps=1e-5, bigram=False)
+    model, W = build(cfg, device)
+    toks = tokens_of(61, vocab=300, seed=16)
+    want = oracle.forward(cfg, W, toks)
+    rp = replayer(model)
+    close(run_cut(rp, "a", toks, [61]), want, TOL[torch.float32])
+    close(run_cut(rp, "b", toks, [3, 2, 40]), want, TOL[torch.float32])
+
+
+@pytest.mark.parametrize("device", DEVICES)
 def test_long_decoding(device):
     cfg = config_of([layer(PAR, FF_B), layer(GRU), layer(PAR, FF_B, weights_of=0)])
     model, W = build(cfg, device)
