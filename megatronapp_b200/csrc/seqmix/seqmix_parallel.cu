@@ -336,8 +336,8 @@ __global__ void __launch_bounds__(kMixThreads) mixed_attention_kernel(MixAttnArg
 // The same attention for head sizes that 16-byte vectors divide (d and dv multiples of 8 for 16-bit, 4 for fp32 activations):
 // a CTA serves up to QB consecutive query tokens of one sequence with the same key tile (a block that straddles two sequences
 // walks them one after the other); key rows are copied and read 16 bytes at a time (rows padded to 128 m + 16 bytes, so a
-// quarter warp's rows fall into distinct banks); a thread owns one (query, key/value head, key) and keeps the key chunk in
-// registers for the heads of the group; values are not staged: in the weighted sum a thread owns 16 bytes of value channels of
+// quarter warp's rows fall into distinct banks); a thread owns one (query, key/value head, pair of keys) and keeps the two key
+// chunks in registers for the heads of the group; values are not staged: in the weighted sum a thread owns 16 bytes of value channels of
 // one head and reads them from the cache once per key for all QB queries.  grid (token blocks, key splits), modes as above.
 // ---------------------------------------------------------------------------------------------------------------------
 template <typename T> struct Vec16;
@@ -443,35 +443,47 @@ __global__ void __launch_bounds__(kMixThreads) mixed_attention_vec_kernel(MixAtt
               *reinterpret_cast<const uint4*>(kc + static_cast<int64_t>(sslot[j]) * G * d + c * VW);
         }
         __syncthreads();
-        for (int e = threadIdx.x; e < nq * G * KT; e += kMixThreads) {   // scores: a thread per (query, key/value head, key)
-          const int j = e % KT, c = (e / KT) % G, qi = e / (KT * G);
-          const bool vis = j < nk && lo + j < slen[qi];
-          const T* kk = sK + static_cast<size_t>(j) * ldk + c * d;
+        // scores: a thread per (query, key/value head, pair of keys KT / 2 apart); the query values it reads from shared memory
+        // serve both keys and the key chunks stay in registers for the heads of the group
+        const int KH = KT / 2;
+        for (int e = threadIdx.x; e < nq * G * KH; e += kMixThreads) {
+          const int ja = e % KH, jb = ja + KH, c = (e / KH) % G, qi = e / (KH * G);
+          const bool va = ja < nk && lo + ja < slen[qi], vb = jb < nk && lo + jb < slen[qi];
+          const T* ka = sK + static_cast<size_t>(ja) * ldk + c * d;
+          const T* kb = sK + static_cast<size_t>(jb) * ldk + c * d;
           for (int hc = 0; hc < rep; hc += kHeadChunk) {
-            float s[kHeadChunk];
+            float sa[kHeadChunk], sb[kHeadChunk];
 #pragma unroll
-            for (int r = 0; r < kHeadChunk; ++r) s[r] = 0.f;
-            if (vis) {
+            for (int r = 0; r < kHeadChunk; ++r) sa[r] = sb[r] = 0.f;
+            if (va) {                                              // vb implies va: visibility ends at one key
               const float* qq = sq + (qi * H + c * rep + hc) * d;
               for (int i = 0; i < d; i += VW) {
-                float kv[VW];
-                Vec16<T>::load(kk + i, kv);
+                float kva[VW], kvb[VW];
+                Vec16<T>::load(ka + i, kva);
+                Vec16<T>::load(kb + i, kvb);                       // a row past the tile's end holds stale, unused data
 #pragma unroll
                 for (int r = 0; r < kHeadChunk; ++r) {
                   if (hc + r < rep) {
 #pragma unroll
                     for (int u = 0; u < VW; u += 4) {
                       const float4 qv = *reinterpret_cast<const float4*>(qq + r * d + i + u);
-                      s[r] = fmaf(qv.x, kv[u], s[r]); s[r] = fmaf(qv.y, kv[u + 1], s[r]);
-                      s[r] = fmaf(qv.z, kv[u + 2], s[r]); s[r] = fmaf(qv.w, kv[u + 3], s[r]);
+                      sa[r] = fmaf(qv.x, kva[u], sa[r]); sb[r] = fmaf(qv.x, kvb[u], sb[r]);
+                      sa[r] = fmaf(qv.y, kva[u + 1], sa[r]); sb[r] = fmaf(qv.y, kvb[u + 1], sb[r]);
+                      sa[r] = fmaf(qv.z, kva[u + 2], sa[r]); sb[r] = fmaf(qv.z, kvb[u + 2], sb[r]);
+                      sa[r] = fmaf(qv.w, kva[u + 3], sa[r]); sb[r] = fmaf(qv.w, kvb[u + 3], sb[r]);
                     }
                   }
                 }
               }
             }
 #pragma unroll
-            for (int r = 0; r < kHeadChunk; ++r)
-              if (hc + r < rep) sS[(qi * H + c * rep + hc + r) * KT + j] = vis ? s[r] : -INFINITY;
+            for (int r = 0; r < kHeadChunk; ++r) {
+              if (hc + r < rep) {
+                float* dst = sS + (qi * H + c * rep + hc + r) * KT;
+                dst[ja] = va ? sa[r] : -INFINITY;
+                dst[jb] = vb ? sb[r] : -INFINITY;
+              }
+            }
           }
         }
         __syncthreads();
